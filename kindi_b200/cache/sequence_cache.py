@@ -4,7 +4,9 @@ Cache entries (one per schedule entry that owns a cache) are grouped by what the
 number of key/value heads of the same size over the same span (all positions, or a window) share one group, and
 each group has storage of its own: a pool of pages ``[entry][page][k|v][kv head][position in page][head_dim]`` and
 a page table ``[slot][block]`` on the device. Entries that ask for a fixed-size state get a 32-bit tensor
-``[slot][...]`` that is zeroed when a slot is taken.
+``[slot][...]`` that is zeroed when a slot is taken. An entry may ask for several things at once (a tuple of needs:
+keys and values for one part of its mixer and states for others): at most one ``KVNeed``, any number of states,
+which ``state_view(entry, k)`` hands out in the order they were asked for.
 
 Lengths are per sequence. A slot is taken when a sequence starts and given back when it ends; pages and slots that
 were given back are handed out again first. The reference's counterpart is one sequence's buffers
@@ -21,6 +23,23 @@ import torch
 
 from ..parts.base import KVNeed, StateNeed
 from .pages import PAGE, CacheError, FreeList, PageMap, pages_for
+
+
+def split_needs(need, entry: int = -1):
+    """(the KVNeed or None, the list of StateNeeds) of what a cache entry asks for: one need, None, or a tuple of them"""
+    items = list(need) if isinstance(need, (tuple, list)) else [need]
+    kv, states = None, []
+    for n in items:
+        if isinstance(n, KVNeed):
+            if kv is not None:
+                raise TypeError("cache entry %d asks for keys and values twice" % entry)
+            kv = n
+        elif isinstance(n, StateNeed):
+            states.append(n)
+        elif n is not None:
+            raise TypeError("cache entry %d asks for %r; a part's cache_need must be KVNeed, StateNeed, None or a "
+                            "tuple of those" % (entry, n))
+    return kv, states
 
 
 @dataclass
@@ -49,17 +68,15 @@ class SequenceCache:
         self.length: List[int] = [0] * self.n_slots
         self.groups: List[KVGroup] = []
         self._where: Dict[int, Tuple[int, int]] = {}          # cache entry -> (group index, index in group)
-        self.state: Dict[int, torch.Tensor] = {}
+        self.state: Dict[int, List[torch.Tensor]] = {}
         by_need: Dict[KVNeed, List[int]] = {}
         for i, need in enumerate(needs):
-            if isinstance(need, KVNeed):
-                by_need.setdefault(need, []).append(i)
-            elif isinstance(need, StateNeed):
-                self.state[i] = torch.zeros((self.n_slots,) + tuple(need.shape), dtype=torch.float32,
-                                            device=self.device)
-            elif need is not None:
-                raise TypeError("cache entry %d asks for %r; a part's cache_need must be KVNeed, StateNeed or None"
-                                % (i, need))
+            kv, states = split_needs(need, i)
+            if kv is not None:
+                by_need.setdefault(kv, []).append(i)
+            if states:
+                self.state[i] = [torch.zeros((self.n_slots,) + tuple(st.shape), dtype=torch.float32,
+                                             device=self.device) for st in states]
         for need, entries in by_need.items():
             n_pool = self.group_pages(need, self.n_pages, self.n_slots, max_step_tokens)
             pool = torch.zeros((len(entries), n_pool, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype,
@@ -90,15 +107,16 @@ class SequenceCache:
         el = torch.empty((), dtype=dtype).element_size()
         total = 0
         seen = set()
-        for need in needs:
-            if isinstance(need, KVNeed):
+        for i, asked in enumerate(needs):
+            need, states = split_needs(asked, i)
+            if need is not None:
                 total += (SequenceCache.group_pages(need, n_pages, n_slots, max_step_tokens) * 2 * need.n_kv_heads
                           * PAGE * need.head_dim * el)
                 if need not in seen:
                     seen.add(need)
                     total += min(n_slots, n_pages) * n_pages * 4
-            elif isinstance(need, StateNeed):
-                total += min(n_slots, n_pages) * int(np.prod(need.shape)) * 4
+            for st in states:
+                total += min(n_slots, n_pages) * int(np.prod(st.shape)) * 4
         return total
 
     def kv_bytes_per_token(self) -> int:
@@ -109,8 +127,9 @@ class SequenceCache:
     def alloc_slot(self) -> int:
         s = self.slots.take()
         self.length[s] = 0
-        for t in self.state.values():
-            t[s].zero_()
+        for ts in self.state.values():
+            for t in ts:
+                t[s].zero_()
         return s
 
     def free_slot(self, slot: int) -> None:
@@ -176,8 +195,9 @@ class SequenceCache:
         g = self.groups[gi]
         return g.pool[j], g.table, g.n_pool_pages
 
-    def state_view(self, entry: int) -> torch.Tensor:
-        return self.state[entry]
+    def state_view(self, entry: int, k: int = 0) -> torch.Tensor:
+        """the k-th state the entry asked for: float32 ``[slots, *shape]``"""
+        return self.state[entry][k]
 
     def tokens_held(self) -> int:
         return max((g.pages.pool.n_held for g in self.groups), default=0) * PAGE

@@ -45,12 +45,15 @@ class ScheduleEntry:
     ``reads_cache_of`` names another schedule entry's cache entry whose keys and values this run attends to
     instead of writing its own. ``add_embedding``: the embedding part's output of this step's rows is added to the
     residual stream right before this run (a model that runs a stretch of layers several times feeds its input in
-    again at the start of every further pass)."""
+    again at the start of every further pass). ``mix_embedding`` (a tensor's full name, ``[width, 2 width]``): right
+    before this run the residual stream is replaced by ``W [x; x0]``, x the stream and x0 the embedding part's
+    output of the step's rows."""
 
     layer: int
     cache: int
     reads_cache_of: Optional[int] = None
     add_embedding: bool = False
+    mix_embedding: Optional[str] = None
 
 
 @dataclass(frozen=True)

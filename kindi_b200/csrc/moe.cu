@@ -20,9 +20,12 @@
 #include <math.h>
 
 #define MOE_MAX_TOP 32
+#define MOE_SCORE_SOFTMAX 0
+#define MOE_SCORE_SIGMOID 1
 
 __global__ void __launch_bounds__(128) k_moe_topk(const float* KB_STEP_DATA logits, int ldz,
-        const float* __restrict__ bias, int T, int E, int top, int* __restrict__ idx, float* __restrict__ wts) {
+        const float* __restrict__ bias, int T, int E, int top, int* __restrict__ idx, float* __restrict__ wts,
+        int score) {
     kb_pdl_launch();
     kb_pdl_wait();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -46,6 +49,14 @@ __global__ void __launch_bounds__(128) k_moe_topk(const float* KB_STEP_DATA logi
         chosen[k] = best;
         val[k] = bv;
     }
+    if (score == MOE_SCORE_SIGMOID) {
+        // every chosen expert keeps its own sigmoid(z); nothing is normalised over the chosen ones
+        for (int k = 0; k < top; k++) {
+            idx[(size_t)t * top + k] = chosen[k];
+            wts[(size_t)t * top + k] = 1.0f / (1.0f + expf(-val[k]));
+        }
+        return;
+    }
     float mx = val[0];
     for (int k = 1; k < top; k++) mx = fmaxf(mx, val[k]);
     float sum = 0.0f;
@@ -64,7 +75,8 @@ __global__ void __launch_bounds__(128) k_moe_topk(const float* KB_STEP_DATA logi
 // by a lane-local scan and five shuffle steps. The chosen values and their softmax are the same bits as k_moe_topk's.
 #define MOE_PER 8
 __global__ void __launch_bounds__(128) k_moe_topk_warp(const float* KB_STEP_DATA logits, int ldz,
-        const float* __restrict__ bias, int T, int E, int top, int* __restrict__ idx, float* __restrict__ wts) {
+        const float* __restrict__ bias, int T, int E, int top, int* __restrict__ idx, float* __restrict__ wts,
+        int score) {
     kb_pdl_launch();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -120,18 +132,20 @@ __global__ void __launch_bounds__(128) k_moe_topk_warp(const float* KB_STEP_DATA
     for (int k = 0; k < top; k++) sum += __shfl_sync(0xffffffffu, ex, k);
     if (lane < top) {
         idx[(size_t)t * top + lane] = my_idx < E ? my_idx : 0;
-        wts[(size_t)t * top + lane] = ex / sum;
+        wts[(size_t)t * top + lane] = score == MOE_SCORE_SIGMOID ? 1.0f / (1.0f + expf(-my_val)) : ex / sum;
     }
 }
 
 extern "C" int kb_moe_topk(const float* logits, int ldz, const float* bias, int T, int E, int top, int* idx,
-                           float* wts, cudaStream_t st) {
+                           float* wts, cudaStream_t st, int score) {
+    // score: MOE_SCORE_SOFTMAX (weights = softmax over the chosen values) or MOE_SCORE_SIGMOID (weights = sigmoid of
+    // each chosen value, not normalised; the order of the values is the order of their sigmoids)
     if (T <= 0) return 0;
     if (top < 1 || top > MOE_MAX_TOP || top > E) return (int)cudaErrorInvalidValue;
     if (E <= 32 * MOE_PER)
-        kb_launch(k_moe_topk_warp, (T + 3) / 4, 128, 0, st, logits, ldz, bias, T, E, top, idx, wts);
+        kb_launch(k_moe_topk_warp, (T + 3) / 4, 128, 0, st, logits, ldz, bias, T, E, top, idx, wts, score);
     else
-        kb_launch(k_moe_topk, (T + 127) / 128, 128, 0, st, logits, ldz, bias, T, E, top, idx, wts);
+        kb_launch(k_moe_topk, (T + 127) / 128, 128, 0, st, logits, ldz, bias, T, E, top, idx, wts, score);
     KB_LAUNCH_RET();
 }
 

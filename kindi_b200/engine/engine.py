@@ -105,7 +105,7 @@ class Engine:
             for n, shape in shapes.items():
                 k = 1
                 for d in shape:
-                    k *= d
+                    k *= abs(d)
                 weights += k * el
         cache = SequenceCache.bytes_needed(cache_needs(spec), self.ctx, self.max_batch, self.dtype,
                                            self.max_step_tokens)

@@ -34,3 +34,14 @@ def attention_from_planes(ctx, qkv, out, nh, nkv, hd, scale, window, rotation, p
     inv_freq, rotary_dim = rotation
     return fast.attention_decode_rope(ctx, qkv, out, nh, nkv, hd, scale, window, inv_freq, rotary_dim, pool, True,
                                       table, n_pages)
+
+
+def sigmoid_attention(ctx, q, out, nh, nkv, hd, scale, bias, pool, table, n_pages) -> None:
+    """``out`` = causal attention whose weights are ``sigmoid(q . k * scale + bias[h][distance])``, not normalised
+    over keys, of the query rows ``q`` over their sequences' cached keys and values (this step's included). ``bias``:
+    float32 ``[nh, n]`` over the distance, the last entry standing for every larger one, or None"""
+    if ctx.fast:
+        from . import fast
+        if fast.sigmoid_attention_bf16(ctx, q, out, nh, nkv, hd, scale, bias, pool, table, n_pages):
+            return
+    K.sigmoid_attn(q, out, ctx.pos, ctx.seq, ctx.slot, nh, nkv, hd, scale, bias, pool, table, n_pages, ctx.status)

@@ -304,23 +304,49 @@ def _moe_tc_ok(y, wup, wdown) -> bool:
             and y.stride(1) == 1 and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0)
 
 
-def _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T):
+def _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T, gated=False, weight_on="output"):
     E, F, width = wup.shape
     h = torch.empty((T * top, F), dtype=torch.bfloat16, device=ys.device)
-    K.moe_gemm_tc(ys, wup, h, plan, None, top, act, up=True, bn=_moe_bn(F, T * top), status=ctx.status)
+    if gated:
+        # [gate | up] of every pair, then act(w g) * (w u) with the pick's weight on the expert's input (or 1)
+        K.moe_gemm_tc(ys, wup, h, plan, None, top, "none", up=True, bn=_moe_bn(F, T * top), status=ctx.status)
+        gu, h = h, torch.empty((T * top, F // 2), dtype=torch.bfloat16, device=ys.device)
+        K.moe_gate_mul(gu, wts if weight_on == "input" else None, plan, act, h)
+    else:
+        K.moe_gemm_tc(ys, wup, h, plan, None, top, act, up=True, bn=_moe_bn(F, T * top), status=ctx.status)
     planes = torch.empty((top, T, width), dtype=torch.float32, device=ys.device)
-    K.moe_gemm_tc(h, wdown, planes, plan, wts, top, "none", up=False, bn=_moe_bn(width, T * top), status=ctx.status)
+    K.moe_gemm_tc(h, wdown, planes, plan, wts if weight_on == "output" else _ones_like(wts), top, "none", up=False,
+                  bn=_moe_bn(width, T * top), status=ctx.status)
     return planes
 
 
-def moe_experts(ctx, y, idx, wts, wup, wdown, top, act):
+_ONES = {}
+
+
+def _ones_like(wts: torch.Tensor) -> torch.Tensor:
+    """weights of one for the down product of experts whose weight sits on their input (kept per size and device)"""
+    key = (wts.numel(), wts.device)
+    t = _ONES.get(key)
+    if t is None:
+        if len(_ONES) > 64:
+            _ONES.clear()
+        t = _ONES[key] = torch.ones(wts.numel(), dtype=torch.float32, device=wts.device)
+    return t
+
+
+def moe_experts(ctx, y, idx, wts, wup, wdown, top, act, gated=False, weight_on="output"):
     """the experts' grouped products on the tensor cores, where the kernel takes the shape (bf16, width and expert
     size multiples of 8): 32-bit planes [top, T, width]; None: not taken"""
     T, width = y.shape
     E, F, _ = wup.shape
-    if not _moe_tc_ok(y, wup, wdown):
+    if not _moe_tc_ok(y, wup, wdown) or (gated and (F // 2) % 8):
         return None
     plan = K.moe_plan(idx, E, K.moe_gemm_tc_tile())
     ys = torch.empty((T * top, width), dtype=torch.bfloat16, device=y.device)
     K.moe_gather(y, ys, plan, top)
-    return _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T)
+    return _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T, gated, weight_on)
+
+
+def sigmoid_attention_bf16(ctx, q, out, nh, nkv, hd, scale, bias, pool, table, n_pages) -> bool:
+    """the serving kernels of attention without a softmax; False: the shape is left to the general kernel"""
+    return False

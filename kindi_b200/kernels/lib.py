@@ -63,7 +63,28 @@ _SIGS = {
     "kb_norm_rope_store": [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
                            c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
-    "kb_moe_topk": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "kb_moe_topk": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int],
+    "kb_sinusoid_add": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "kb_mix_cat": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "kb_short_conv": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                      c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                      c_void_p],
+    "kb_delta_rule": [c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p,
+                      c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                      c_int, c_void_p],
+    "kb_head_norm_gate": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_longlong,
+                          c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+    "kb_min_gru": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                   c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p],
+    "kb_branch_norm_mean": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
+                            c_void_p],
+    "kb_moe_gate_mul": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "kb_row_gate": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "kb_sigattn_prep": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                        c_void_p, c_void_p],
+    "kb_sigmoid_attn": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "kb_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "kb_moe_gemm_tile": [],
     "kb_moe_gemm_tc_tile": [],
@@ -477,11 +498,19 @@ def decay_scan(a: torch.Tensor, B: int, H: int, d: int, dv: int, decay: torch.Te
                                 _p(state), _p(out), out.stride(0), _stream()), "decay_scan")
 
 
-def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
-    """the ``top`` largest of each row of logits + bias (float32 [T, E]) and the softmax over those alone:
-    (idx int32 [T, top], weights float32 [T, top])"""
+MOE_SCORE = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, score: str = "softmax",
+             n_experts: Optional[int] = None):
+    """the ``top`` largest of each row of logits + bias (float32 [T, >= E]; ``n_experts``: the first E columns are
+    the experts') and their weights: the softmax over those alone (``score`` "softmax") or each one's own sigmoid, not
+    normalised ("sigmoid"): (idx int32 [T, top], weights float32 [T, top])"""
     _need_cuda(logits, bias)
     T, E = logits.shape
+    if n_experts is not None:
+        assert n_experts <= E
+        E = n_experts
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous()
@@ -489,8 +518,8 @@ def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
         raise KernelError("kindi_b200: a row picks 1 to 32 of its %d experts, found top = %d" % (E, top))
     idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    _check(load().kb_moe_topk(_p(logits), logits.stride(0), _p(bias), T, E, top, _p(idx), _p(wts), _stream()),
-           "moe_topk")
+    _check(load().kb_moe_topk(_p(logits), logits.stride(0), _p(bias), T, E, top, _p(idx), _p(wts), _stream(),
+                              MOE_SCORE[score]), "moe_topk")
     return idx, wts
 
 
@@ -821,3 +850,177 @@ def attn_tc(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, n
                              hd, float(scale), int(window), _p(pool), _p(table), table.stride(0), n_pages, grid_x,
                              _p(status), _stream(), int(keep_first), _p(sink), _p(gate),
                              gate.stride(0) if gate is not None else 0), "attn_tc")
+
+
+# ----------------------------------------------------------------------------------------------- stateful mixers
+GATE_KIND = {"none": 0, "sigmoid": 1, "silu": 2}
+
+
+def sinusoid_add(x: torch.Tensor, pos: torch.Tensor, freq: torch.Tensor) -> None:
+    """x[t][2i] += sin(pos[t] * freq[i]), x[t][2i + 1] += cos(pos[t] * freq[i]); x float32 [T, E], freq float64"""
+    _need_cuda(x, pos, freq)
+    T, E = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and freq.dtype == torch.float64 and freq.is_contiguous()
+    assert freq.numel() >= (E + 1) // 2 and pos.dtype == torch.int32
+    _check(load().kb_sinusoid_add(_p(x), _p(pos), _p(freq), T, E, _stream()), "sinusoid_add")
+
+
+def mix_cat(x: torch.Tensor, delta: Optional[torch.Tensor], scale: Optional[torch.Tensor], x0: torch.Tensor,
+            out: torch.Tensor) -> None:
+    """out[t] = [x[t] + scale * (sum of delta's planes)[t] | x0[t]]; x, x0 float32 [T, E], out [T, 2 E]"""
+    _need_cuda(x, delta, scale, x0, out)
+    T, E = x.shape
+    assert x.dtype == x0.dtype == torch.float32 and x.is_contiguous() and x0.is_contiguous() and x0.shape == x.shape
+    assert out.is_contiguous() and out.shape == (T, 2 * E)
+    nd, stride = 0, 0
+    if delta is not None:
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and delta.shape[1:] == (T, E)
+        nd, stride = delta.shape[0], T * E
+    if scale is not None:
+        assert scale.dtype == torch.float32 and scale.is_contiguous() and scale.numel() == E
+    _check(load().kb_mix_cat(_p(x), _p(delta), nd, stride, _p(scale) if delta is not None else None, _p(x0), _p(out),
+                             dt(out), T, E, _stream()), "mix_cat")
+
+
+def short_conv(a: torch.Tensor, col0: int, C: int, bias: Optional[torch.Tensor], w: torch.Tensor, act: bool,
+               tails: torch.Tensor, pos, seq, slot, q_start, out: torch.Tensor) -> None:
+    """causal convolution over time per channel on columns ``col0 .. col0 + C`` of ``a`` (rows or 32-bit planes), plus
+    ``bias`` before the convolution; ``w`` float32 [C, taps] (the last tap meets the current token); ``act``: silu
+    after it. ``tails``: float32 [slots, >= (taps - 1) * C] (a view whose rows may be strided), the sequence's last
+    taps - 1 inputs, read for positions before this step and rewritten. ``out`` [T, C] (a view is fine)"""
+    _need_cuda(a, bias, w, tails, out)
+    n_planes, pstride, ld = _planes_of(a)
+    T = a.shape[-2]
+    taps = w.shape[1]
+    assert w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == C and a.shape[-1] >= col0 + C
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C)
+    assert tails.dtype == torch.float32 and tails.stride(1) == 1 and tails.shape[1] >= (taps - 1) * C
+    assert out.shape == (T, C) and out.stride(1) == 1
+    if not (1 <= taps <= 8):
+        raise KernelError("kindi_b200: a short convolution has 1 to 8 taps, found %d" % taps)
+    _check(load().kb_short_conv(_p(a), dt(a), n_planes, pstride, ld, col0, C, _p(bias), _p(w), taps, 1 if act else 0,
+                                _p(tails), tails.stride(0), _p(pos), _p(seq), _p(slot), _p(q_start), _p(out), dt(out),
+                                out.stride(0), T, _stream()), "short_conv")
+
+
+def delta_rule(qkv: torch.Tensor, proj: torch.Tensor, ob: int, oa: int, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               B: int, H: int, G: int, d: int, dv: int, unit_eps: float, q_start, slot, state: torch.Tensor,
+               out: torch.Tensor) -> None:
+    """the gated delta rule over the packed rows of ``B`` sequences. ``qkv`` float32 rows [q (G d) | k (G d) | v (H dv)];
+    ``proj`` (rows or 32-bit planes) holds the beta logits at columns ``ob ..`` and the decay's at ``oa ..`` (H each);
+    ``state`` float32 [slots, >= H dv d] (rows may be strided) is read and written; ``out`` float32 [T, H dv]"""
+    _need_cuda(qkv, proj, a_log, dt_bias, state, out)
+    n_planes, pstride, ldp = _planes_of(proj)
+    assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] >= 2 * G * d + H * dv
+    assert a_log.dtype == dt_bias.dtype == torch.float32 and a_log.numel() == H == dt_bias.numel()
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= H * dv * d
+    assert out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == H * dv
+    if d > 256:
+        raise KernelError("kindi_b200: the delta rule supports key sizes up to 256, found %d" % d)
+    _check(load().kb_delta_rule(_p(qkv), qkv.stride(0), _p(proj), dt(proj), n_planes, pstride, ldp, ob, oa, _p(a_log),
+                                _p(dt_bias), B, H, G, d, dv, float(unit_eps), _p(q_start), _p(slot), _p(state),
+                                state.stride(0), _p(out), out.stride(0), _stream()), "delta_rule")
+
+
+def head_norm_gate(x: torch.Tensor, H: int, n: int, w: torch.Tensor, eps: float, g: Optional[torch.Tensor], og: int,
+                   gate: str, out: torch.Tensor) -> None:
+    """out[t][h n + e] = x[t][h n + e] / sqrt(mean_e x^2 + eps) * w[e] * gate(g[t][og + h n + e]); x float32 [T, H n],
+    w float32 [n], ``g`` rows or 32-bit planes, ``gate``: none, sigmoid or silu"""
+    _need_cuda(x, w, g, out)
+    T = x.shape[0]
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and x.shape[1] == H * n and w.dtype == torch.float32
+    assert w.numel() == n and w.is_contiguous() and out.shape == (T, H * n) and out.stride(1) == 1
+    n_planes, pstride, ldg = _planes_of(g) if g is not None else (1, 0, 0)
+    _check(load().kb_head_norm_gate(_p(x), x.stride(0), T, H, n, _p(w), float(eps), _p(g),
+                                    dt(g) if g is not None else F32, n_planes, pstride, ldg, og, GATE_KIND[gate],
+                                    _p(out), dt(out), out.stride(0), _stream()), "head_norm_gate")
+
+
+def min_gru(a: torch.Tensor, oz: int, ox: int, og: int, W: int, bz: Optional[torch.Tensor],
+            bx: Optional[torch.Tensor], B: int, q_start, slot, state: torch.Tensor, out: torch.Tensor) -> None:
+    """S <- (1 - z) S + z c per element over the packed rows of ``B`` sequences: z = sigmoid(a[oz ..] + bz),
+    u = a[ox ..] + bx, c = u + 1/2 where u >= 0 else sigmoid(u); out = S * silu(a[og ..]). ``state`` float32
+    [slots, >= W] (rows may be strided)"""
+    _need_cuda(a, bz, bx, state, out)
+    n_planes, pstride, ld = _planes_of(a)
+    T = a.shape[-2]
+    for b_ in (bz, bx):
+        assert b_ is None or (b_.dtype == torch.float32 and b_.is_contiguous() and b_.numel() == W)
+    assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= W
+    assert out.shape == (T, W) and out.stride(1) == 1
+    _check(load().kb_min_gru(_p(a), dt(a), n_planes, pstride, ld, oz, ox, og, W, _p(bz), _p(bx), B, _p(q_start),
+                             _p(slot), _p(state), state.stride(0), _p(out), dt(out), out.stride(0), _stream()),
+           "min_gru")
+
+
+def branch_norm_mean(branches, eps: float, out: torch.Tensor) -> None:
+    """out (float32 [T, E]) = the mean over ``branches`` of rms(sum of planes + bias) * gain; each branch is
+    ``(planes float32 [S, T, E], bias float32 [E] or None, gain float32 [E])``, at most four"""
+    n = len(branches)
+    T, E = out.shape
+    assert 1 <= n <= 4 and out.dtype == torch.float32 and out.is_contiguous()
+    ptrs, counts, strides, biases, gains = [], [], [], [], []
+    for planes, bias, gain in branches:
+        _need_cuda(planes, bias, gain)
+        assert planes.dtype == torch.float32 and planes.is_contiguous() and planes.shape[1:] == (T, E)
+        assert gain.dtype == torch.float32 and gain.is_contiguous() and gain.numel() == E
+        assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == E)
+        ptrs.append(_p(planes))
+        counts.append(planes.shape[0])
+        strides.append(T * E)
+        biases.append(_p(bias))
+        gains.append(_p(gain))
+    arr = (c_void_p * n)
+    _check(load().kb_branch_norm_mean(n, arr(*ptrs), (c_int * n)(*counts), (c_longlong * n)(*strides), arr(*biases),
+                                      arr(*gains), float(eps), _p(out), T, E, _stream()), "branch_norm_mean")
+
+
+def moe_gate_mul(gu: torch.Tensor, wts: Optional[torch.Tensor], plan: "MoePlan", act: str, h: torch.Tensor) -> None:
+    """h[r] = act(w g) * (w u) over the plan's sorted rows: ``gu`` [n_pairs, 2 F] = [gate | up], w = the weight of the
+    row's (token, pick) pair"""
+    _need_cuda(gu, wts, h)
+    n, F2 = gu.shape
+    F = F2 // 2
+    assert gu.stride(1) == 1 and h.shape == (n, F) and h.stride(1) == 1 and h.dtype == gu.dtype and n == plan.n_pairs
+    assert wts is None or (wts.dtype == torch.float32 and wts.is_contiguous() and wts.numel() == n)
+    _check(load().kb_moe_gate_mul(_p(gu), dt(gu), gu.stride(0), _p(wts), _p(plan.perm), n, F, ACT[act], _p(h),
+                                  h.stride(0), _stream()), "moe_gate_mul")
+
+
+def row_gate(h: torch.Tensor, z: torch.Tensor) -> None:
+    """h[t] *= sigmoid(z[t]); ``z`` float32 [T] (a strided view is fine); in place"""
+    _need_cuda(h, z)
+    T, N = h.shape
+    assert h.stride(1) == 1 and z.dtype == torch.float32 and z.numel() == T and z.dim() == 1
+    _check(load().kb_row_gate(_p(h), dt(h), h.stride(0), _p(z), z.stride(0), T, N, _stream()), "row_gate")
+
+
+def sigattn_prep(c: torch.Tensor, H: int, G: int, d: int, dv: int, hd: int, coef: float, every: int, v_norm: bool,
+                 eps: float, pos, seq, slot, q_out: torch.Tensor, pool: torch.Tensor, table: torch.Tensor, n_pages: int,
+                 status: torch.Tensor) -> None:
+    """``c`` float32 rows [q (H d) | k (G d) | v (G dv)]: queries times ``1 + coef ln((pos + 1) // every + 1)`` to
+    ``q_out`` [T, H hd]; keys, and values divided per head by their root mean square (``v_norm``), into the cache"""
+    _need_cuda(c, q_out, pool, table)
+    T = c.shape[0]
+    assert c.dtype == torch.float32 and c.stride(1) == 1 and c.shape[1] >= H * d + G * d + G * dv
+    assert q_out.shape == (T, H * hd) and q_out.stride(1) == 1 and pool.dtype == q_out.dtype and pool.is_contiguous()
+    assert pool.shape[-1] == hd and pool.shape[-3] == G
+    _check(load().kb_sigattn_prep(_p(c), c.stride(0), T, H, G, d, dv, hd, float(coef), int(every), 1 if v_norm else 0,
+                                  float(eps), _p(pos), _p(seq), _p(slot), _p(q_out), dt(q_out), q_out.stride(0),
+                                  _p(pool), _p(table), table.stride(0), n_pages, _p(status), _stream()), "sigattn_prep")
+
+
+def sigmoid_attn(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nkv: int, hd: int, scale: float,
+                 bias: Optional[torch.Tensor], pool: torch.Tensor, table: torch.Tensor, n_pages: int,
+                 status: torch.Tensor) -> None:
+    """causal attention whose weights are sigmoid(q . k * scale + bias[h][distance]) without normalisation (the
+    general kernel); ``bias`` float32 [nh, n] over the distance, its last entry for every larger distance, or None"""
+    _need_cuda(q, out, bias, pool, table)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == pool.dtype and pool.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape[0] == nh)
+    if hd > 512:
+        raise KernelError("kindi_b200: head sizes up to 512 are supported, found %d" % hd)
+    _check(load().kb_sigmoid_attn(_p(q), dt(q), q.stride(0), _p(out), out.stride(0), _p(pos), _p(seq), _p(slot), T, nh,
+                                  nkv, hd, float(scale), _p(bias), bias.shape[1] if bias is not None else 0, _p(pool),
+                                  _p(table), table.stride(0), n_pages, _p(status), _stream()), "sigmoid_attn")

@@ -79,10 +79,21 @@ class StepContext:
 class Branch:
     """a branch output not yet added to the residual: ``parts`` is 32-bit ``[S, T, width]``; the sum over S, taken
     in order, is the branch. ``scale`` (``[width]``, the norm gains' dtype; None for none): the sum is multiplied by it,
-    column by column, before it joins the residual (a model's learned per-column scale of a sub-layer's output)"""
+    column by column, before it joins the residual (a model's learned per-column scale of a sub-layer's output).
+    ``bias`` (float32 ``[width]`` or None): counts once in the sum of the planes (an output projection's bias); a
+    consumer that adds planes only asks for ``with_bias_plane()``"""
 
     parts: torch.Tensor
     scale: Optional[torch.Tensor] = None
+    bias: Optional[torch.Tensor] = None
+
+    def with_bias_plane(self) -> "Branch":
+        """the same branch with the bias as one more plane (the branch itself when it has none)"""
+        if self.bias is None:
+            return self
+        S, T, W = self.parts.shape
+        plane = self.bias.to(torch.float32).view(1, 1, W).expand(1, T, W)
+        return Branch(torch.cat([self.parts, plane], dim=0), self.scale, None)
 
 
 # ----------------------------------------------------------------------------- tensors by name
@@ -193,9 +204,14 @@ class PositionEncoding(Part):
 class Mixer(Part):
     category = "mixer"
 
+    # the index of this mixer's first state among its cache entry's states: 0 for a mixer that owns the entry; a mixer
+    # that runs other mixers side by side gives each of them the place where its states begin
+    state_base = 0
+
     @classmethod
     def cache_need(cls, spec: PartSpec, width: int):
-        """``KVNeed``, ``StateNeed`` or None"""
+        """``KVNeed``, ``StateNeed``, None, or a tuple of those (at most one ``KVNeed``): the states are handed out
+        by ``ctx.cache.state_view(entry, self.state_base + k)`` in the order they stand here"""
         return None
 
     def forward(self, ctx: StepContext, y: torch.Tensor) -> Branch:

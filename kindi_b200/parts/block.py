@@ -12,6 +12,8 @@ from __future__ import annotations
 
 from typing import Dict, Optional, Tuple
 
+import torch
+
 from ..config.registry import part_class, register_part
 from ..config.spec import PartSpec
 from .base import Block, Branch, StepContext, WeightView
@@ -91,7 +93,7 @@ class PreNormBlock(Block):
 
     def forward(self, ctx: StepContext, x, pending: Optional[Branch]) -> Optional[Branch]:
         y = self.norm1.add_norm(ctx, x, pending)
-        pending = self.mixer.forward(ctx, y)
+        pending = self.mixer.forward(ctx, y).with_bias_plane()
         pending.scale = self.scale1
         if self.feed_forward is None:
             return pending
@@ -104,4 +106,33 @@ class PreNormBlock(Block):
         return sum(p.bytes_read() for p in self._parts())
 
 
+class ParallelBlock(PreNormBlock):
+    """mixer and feed-forward side by side on the same residual: ``x += m * (mixer(norm1(x)) + feed_forward(norm2(x)))``,
+    each with a norm of its own. ``residual_mult`` (m, default 1) is a parameter; without a feed-forward the block is
+    ``x += m * mixer(norm1(x))``. The block returns ONE pending branch: the mixer's planes followed by the
+    feed-forward's, with m as the branch's per-column scale, so the next norm adds ``m * (sum of the planes)``."""
+
+    def __init__(self, spec, width, weights: WeightView, *, dtype, device):
+        super().__init__(spec, width, weights, dtype=dtype, device=device)
+        if self.scale1 is not None or self.scale2 is not None:
+            raise ValueError("a parallel block has one residual multiplier, not a learned scale per sub-layer")
+        m = float(spec.get("residual_mult", 1.0))
+        self.mult = None if m == 1.0 else torch.full((width,), m, dtype=torch.float32, device=device)
+
+    def forward(self, ctx: StepContext, x, pending: Optional[Branch]) -> Optional[Branch]:
+        y1 = self.norm1.add_norm(ctx, x, pending)              # (adds the pending branch into x)
+        y2 = self.norm2.add_norm(ctx, x, None) if self.feed_forward is not None else None
+        a = self.mixer.forward(ctx, y1).with_bias_plane()
+        if a.scale is not None:
+            raise NotImplementedError("a scaled branch inside a parallel block")
+        planes = a.parts
+        if self.feed_forward is not None:
+            b = self.feed_forward.forward(ctx, y2)
+            if b.scale is not None:
+                raise NotImplementedError("a scaled branch inside a parallel block")
+            planes = torch.cat([a.parts, b.parts], dim=0)
+        return Branch(planes, self.mult)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)

@@ -2,7 +2,9 @@
 
 ``x[t] = table[tok[t]]``, the row as stored, without the scaling by the square root of the width that some
 architectures apply (``kindi/nbq.cu:472-487``; ``kindi/nanbeige.py:577,681``); an architecture that does scale gives
-``scale``. The tensor's full name, the vocabulary size and the scale are parameters of the part. An architecture
+``scale``. With ``sinusoid`` (``{"base": 10000.0}``) a position vector is added to the scaled row: column 2i gets
+``sin(p * base^(-2i / width))`` and column 2i + 1 the cosine of the same angle, p the row's position in its sequence
+(angles and functions in 64-bit). The tensor's full name, the vocabulary size and the scale are parameters of the part. An architecture
 whose front end is something else (a learned position table added in, several tables) registers its own part of the
 category "embedding" with the same ``forward``.
 """
@@ -27,10 +29,18 @@ class TokenEmbedding(Embedding):
         super().__init__(spec, width, weights, dtype=dtype, device=device)
         self.table = weights(spec["name"])
         self.scale = float(spec.get("scale") or 1.0)
+        self.freq = None
+        sin = spec.get("sinusoid")
+        if sin:
+            base = float(sin.get("base", 10000.0))
+            self.freq = torch.tensor([base ** (-2.0 * i / width) for i in range((width + 1) // 2)],
+                                     dtype=torch.float64, device=device)
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         x = torch.empty((ctx.T, self.width), dtype=torch.float32, device=self.table.device)
         K.embed(self.table, ctx.tok, x, ctx.status, self.scale)
+        if self.freq is not None:
+            K.sinusoid_add(x, ctx.pos, self.freq)
         return x
 
     def bytes_read(self, n_rows: int = 0) -> int:

@@ -13,6 +13,7 @@ import torch
 from ..config.registry import part_class
 from ..config.spec import ModelSpec
 from ..kernels import lib as K
+from ..kernels import linear as L
 from .base import Branch, StepContext, WeightView
 
 
@@ -33,6 +34,12 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[int, ...]]:
             name, shape = prefix + suffix, tuple(int(n) for n in shape)
             if out.setdefault(name, shape) != shape:
                 raise ValueError("tensor %s is asked for with shapes %s and %s" % (name, out[name], shape))
+    for e in spec.schedule:
+        if e.mix_embedding is not None:
+            shape = (spec.width, 2 * spec.width)
+            if out.setdefault(e.mix_embedding, shape) != shape:
+                raise ValueError("tensor %s is asked for with shapes %s and %s" % (e.mix_embedding,
+                                                                                  out[e.mix_embedding], shape))
     return out
 
 
@@ -70,15 +77,24 @@ class DecoderModel:
         self.final_norm = make("norm", spec.final_norm, spec.final_norm_prefix)
         self.head = make("head", spec.head, "")
         self.graph_safe = all(p.graph_safe for p in [self.embedding, self.final_norm, self.head] + self.blocks)
+        self.mixers = {e.mix_embedding: tensors[e.mix_embedding] for e in spec.schedule if e.mix_embedding is not None}
 
     def forward(self, ctx: StepContext, rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """run the step's tokens through every scheduled layer (keys, values and state are stored on the way);
         returns 32-bit logits ``[len(rows), vocab]`` of the listed rows, or None when no row is wanted"""
         x = self.embedding.forward(ctx)
         # a schedule that feeds the embedding output in again needs it as it was: the norms update x in place
-        x0 = self.embedding.forward(ctx) if any(e.add_embedding for e in self.spec.schedule) else None
+        x0 = self.embedding.forward(ctx) if any(e.add_embedding or e.mix_embedding is not None
+                                                for e in self.spec.schedule) else None
         pending: Optional[Branch] = None
         for entry in self.spec.schedule:
+            if entry.mix_embedding is not None:
+                # x <- W [x + pending branch; x0]: one row of both, then the product with 32-bit output
+                both = torch.empty((ctx.T, 2 * self.spec.width), dtype=self.dtype, device=x.device)
+                scale = None if pending is None or pending.scale is None else pending.scale.to(torch.float32)
+                K.mix_cat(x, None if pending is None else pending.parts, scale, x0, both)
+                x = L.linear(ctx, both, self.mixers[entry.mix_embedding], torch.float32)
+                pending = None
             if entry.add_embedding:
                 if pending is not None and pending.scale is not None:
                     raise NotImplementedError("a scaled branch cannot be pending where the embedding is added again")
@@ -96,4 +112,6 @@ class DecoderModel:
         """weight bytes one step reads: every scheduled layer once, the head once, n_rows embedding rows"""
         per_layer = [b.bytes_read() for b in self.blocks]
         total = sum(per_layer[e.layer] for e in self.spec.schedule)
+        total += sum(self.mixers[e.mix_embedding].numel() * self.mixers[e.mix_embedding].element_size()
+                     for e in self.spec.schedule if e.mix_embedding is not None)
         return total + self.final_norm.bytes_read() + self.head.bytes_read() + self.embedding.bytes_read(n_rows)

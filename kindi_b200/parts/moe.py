@@ -9,6 +9,17 @@ expert, already weighted), which the next norm adds in order, so every row's sum
 All rows of a step go through the experts as grouped products over (row, pick) pairs sorted by expert; the sort
 happens on the device, so the part can be recorded. Sizes, the activation, whether the router has a bias and the
 tensors' suffixes (``router``, ``router_bias``, ``up`` and ``down`` with ``%d`` for the expert) are parameters.
+
+Further options, all parameters:
+
+* ``gated``: an expert is ``W_down (act(W_gate y) * (W_up y))`` (suffix ``gate``, with ``%d``).
+* ``score`` = ``sigmoid``: the weights are the chosen experts' own ``sigmoid(z)``, not normalised over the chosen
+  ones (the order of the logits is the order of their sigmoids, so the pick is the same).
+* ``weight_on`` = ``input`` (gated experts): the weight multiplies the expert's input, ``expert(w y)``, which is
+  ``W_down (act(w g) * (w u))`` with ``g = W_gate y``, ``u = W_up y``.
+* ``shared`` (``{"intermediate", "activation", "names": {gate, up, down}, "row_gate": suffix or None}``): a gated
+  feed-forward that every row passes through, added as one more plane; with ``row_gate`` (a ``[1, width]`` tensor)
+  it is multiplied by ``sigmoid(W_sg y)``, one number per row, whose logit rides in the router's product.
 """
 from __future__ import annotations
 
@@ -19,11 +30,13 @@ import torch
 from ..config.registry import register_part
 from ..config.spec import PartSpec
 from ..kernels import lib as K
+from ..kernels import linear as L
 from ..kernels import moe as M
 from .base import Branch, FeedForward, StepContext, WeightView
 
 _DEFAULT_NAMES = {"router": "router.weight", "router_bias": "router.bias", "up": "experts.%d.up_proj.weight",
-                  "down": "experts.%d.down_proj.weight"}
+                  "down": "experts.%d.down_proj.weight", "gate": "experts.%d.gate_proj.weight"}
+_SHARED_NAMES = {"gate": "shared.gate_proj.weight", "up": "shared.up_proj.weight", "down": "shared.down_proj.weight"}
 
 
 class MixtureOfExperts(FeedForward):
@@ -47,7 +60,22 @@ class MixtureOfExperts(FeedForward):
         for e in range(E):
             out[n["up"] % e] = (f, width)
             out[n["down"] % e] = (width, f)
+            if spec.get("gated"):
+                out[n["gate"] % e] = (f, width)
+        sh = spec.get("shared")
+        if sh:
+            sn = cls._shared_names(sh)
+            fs = int(sh["intermediate"])
+            out.update({sn["gate"]: (fs, width), sn["up"]: (fs, width), sn["down"]: (width, fs)})
+            if sh.get("row_gate"):
+                out[sh["row_gate"]] = (1, width)
         return out
+
+    @classmethod
+    def _shared_names(cls, sh):
+        n = dict(_SHARED_NAMES)
+        n.update(sh.get("names") or {})
+        return n
 
     @classmethod
     def tensor_init(cls, spec: PartSpec, width: int) -> Dict[str, str]:
@@ -68,16 +96,54 @@ class MixtureOfExperts(FeedForward):
         downs = [weights(n["down"] % e) for e in range(self.E)]
         if len({w.dtype for w in ups + downs}) != 1:
             raise ValueError("the expert weights of %s are stored in different dtypes" % weights.prefix)
-        self.wup = torch.stack(ups).contiguous()            # [E, f, width]
+        self.gated = bool(spec.get("gated"))
+        self.score = str(spec.get("score") or "softmax")
+        self.weight_on = str(spec.get("weight_on") or "output")
+        if self.score not in K.MOE_SCORE:
+            raise ValueError("unknown router score %r; known: %s" % (self.score, ", ".join(sorted(K.MOE_SCORE))))
+        if self.weight_on not in ("output", "input") or (self.weight_on == "input" and not self.gated):
+            raise ValueError("weight_on is 'output', or 'input' for gated experts; found %r" % self.weight_on)
+        if self.gated:
+            gates = [weights(n["gate"] % e) for e in range(self.E)]
+            if {w.dtype for w in gates} != {ups[0].dtype}:
+                raise ValueError("the expert weights of %s are stored in different dtypes" % weights.prefix)
+            ups = [torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]      # every expert: its gate rows, then up
+        self.wup = torch.stack(ups).contiguous()            # [E, f (gated: 2 f), width]
         self.wdown = torch.stack(downs).contiguous()        # [E, width, f]
+        self.shared = None
+        sh = spec.get("shared")
+        if sh:
+            sn = self._shared_names(sh)
+            act = str(sh.get("activation") or "silu")
+            wgu, group = L.join_gate_up(weights(sn["gate"]), weights(sn["up"]))
+            self.shared = (wgu, group, int(sh["intermediate"]), act, weights(sn["down"]))
+            self.row_gate = bool(sh.get("row_gate"))
+            if self.row_gate:
+                # the gate's logit is one more row of the router's product (zero rows fill up to a multiple of eight)
+                rows = [self.wr, weights(sh["row_gate"]).to(self.wr.dtype)]
+                pad = -(self.E + 1) % 8
+                if pad:
+                    rows.append(torch.zeros((pad, width), dtype=self.wr.dtype, device=self.wr.device))
+                self.wr = torch.cat(rows, dim=0).contiguous()
 
     def forward(self, ctx: StepContext, y: torch.Tensor) -> Branch:
-        return Branch(M.feed_forward(ctx, y, self.wr, self.br, self.wup, self.wdown, self.top, self.act, self.dtype))
+        out = M.feed_forward(ctx, y, self.wr, self.br, self.wup, self.wdown, self.top, self.act, self.dtype,
+                             score=self.score, gated=self.gated, weight_on=self.weight_on,
+                             n_experts=self.E if self.shared is not None and self.row_gate else None)
+        if self.shared is None:
+            return Branch(out)
+        planes, logits = out if self.row_gate else (out, None)
+        wgu, group, fs, act, wd = self.shared
+        h = L.gate_up_swiglu(ctx, y, wgu, group, fs, self.dtype, act)
+        if logits is not None:
+            K.row_gate(h, logits[:, self.E])            # W_down (s h) = s W_down h: the gate scales the row once
+        return Branch(torch.cat([planes, L.planes(ctx, h, wd)], dim=0))
 
     def bytes_read(self) -> int:
         """the router and, of the experts, the share a single row reads (a large step reads up to all of them)"""
         per_expert = (self.wup.numel() + self.wdown.numel()) // self.E * self.wup.element_size()
-        return self.wr.numel() * self.wr.element_size() + self.top * per_expert
+        shared = 0 if self.shared is None else (self.shared[0].numel() + self.shared[4].numel()) * self.wup.element_size()
+        return self.wr.numel() * self.wr.element_size() + self.top * per_expert + shared
 
 
 register_part("feed_forward", "moe", MixtureOfExperts)

@@ -3,7 +3,8 @@
 ``v = x + pending branch`` (written back to the 32-bit residual), ``y = (rsqrt(mean(v^2) + eps) * v) * w`` with the
 sum of squares, the scale and both products in 32-bit - the reference's ``nbq_add_rms_q8`` (``kindi/nbq.cu:412-432``)
 and, for the final norm on the rows whose logits are wanted, ``nbq_add_rms`` (``kindi/nbq.cu:435-453``). The weight
-multiplies as stored (no ``1 + w``). ``eps`` is a parameter of the part.
+multiplies as stored (no ``1 + w``) unless the part's ``one_plus`` is set: the stored weight then lies around zero and
+the gain is ``1 + w``, made once in 32-bit when the part is built. ``eps`` is a parameter of the part.
 """
 from __future__ import annotations
 
@@ -18,7 +19,8 @@ from .base import Branch, Norm, StepContext, WeightView
 
 
 class RMSNorm(Norm):
-    """``eps`` and the gain's suffix (``weight``, default "weight") are parameters of the part"""
+    """``eps``, the gain's suffix (``weight``, default "weight") and ``one_plus`` (the gain is 1 + the stored weight)
+    are parameters of the part"""
 
     @classmethod
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
@@ -26,12 +28,15 @@ class RMSNorm(Norm):
 
     @classmethod
     def tensor_init(cls, spec: PartSpec, width: int) -> Dict[str, str]:
-        return {spec.get("weight", "weight"): "gain"}
+        # (a weight stored around zero is drawn like any other tensor)
+        return {} if spec.get("one_plus") else {spec.get("weight", "weight"): "gain"}
 
     def __init__(self, spec, width, weights: WeightView, *, dtype, device):
         super().__init__(spec, width, weights, dtype=dtype, device=device)
         self.eps = float(spec["eps"])
         self.weight = weights(spec.get("weight", "weight"))
+        if spec.get("one_plus"):
+            self.weight = (1.0 + self.weight.to(torch.float32)).contiguous()
 
     def add_norm(self, ctx: StepContext, x, pending: Optional[Branch], rows=None):
         n_out = x.shape[0] if rows is None else rows.numel()

@@ -49,7 +49,8 @@ def target_dtype(stored: torch.dtype, run_dtype: str) -> torch.dtype:
 def load_tensors(model_dir: str, expected: Mapping[str, Tuple[int, ...]], *, run_dtype: str = "bfloat16",
                  device: str = "cpu", may_ignore: Sequence[str] = (), copies: Optional[Mapping[str, str]] = None,
                  log=None) -> Dict[str, torch.Tensor]:
-    """read the tensors named in ``expected`` (name -> shape) from the folder's safetensors files.
+    """read the tensors named in ``expected`` (name -> shape; a negative size stands for "any positive size": the
+    tensor's own shape then gives it, e.g. the rows of a table) from the folder's safetensors files.
 
     ``may_ignore``: ``fnmatch`` patterns of names the folder may hold that the model does not read. ``copies``:
     ``{name: other}``: the folder may hold ``name`` only as a bit-for-bit copy of ``other`` (a tied head stored
@@ -87,7 +88,7 @@ def load_tensors(model_dir: str, expected: Mapping[str, Tuple[int, ...]], *, run
     for n, shape in expected.items():
         if n in where:
             dt, found = where[n].entries[n]
-            if tuple(found) != tuple(shape):
+            if len(found) != len(shape) or any(e != f and not (e < 0 and f > 0) for e, f in zip(shape, found)):
                 wrong_shape.append((n, tuple(shape), tuple(found)))
             if dt == "BOOL":
                 wrong_dtype.append((n, dt))

@@ -45,7 +45,8 @@ def random_tensors(expected: Mapping[str, Tuple[int, ...]], seed: int, *, std: f
     """``inits``: name -> "gain" | "zero" for the tensors that are not drawn around zero (``parts.model.tensor_inits``
     collects what the parts say)"""
     inits = inits or {}
-    return {n: random_tensor(n, tuple(s), seed, std, dtype, device, inits.get(n, "normal"))
+    # (a negative size means "any positive size": the random model takes its absolute value)
+    return {n: random_tensor(n, tuple(abs(int(d)) for d in s), seed, std, dtype, device, inits.get(n, "normal"))
             for n, s in expected.items()}
 
 
