@@ -420,6 +420,68 @@ def bench_nilatar(a) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- --arch medodra
+# Layer sizes that resemble real models' (random weights, four layers: the side-by-side mixer of attention without a
+# softmax and minGRU, the gated delta rule, and both once more; each with a mixture of gated silu experts, two of
+# eight per token plus a gated shared expert, whose active size equals the dense feed-forward's), each beside the
+# Nilatar design (the closest one: a hybrid of attention and a recurrent layer) of the same width, heads, head size
+# and active feed-forward size.
+MEDODRA_EXPERTS, MEDODRA_TOP, MEDODRA_CONV, MEDODRA_FAR = 8, 2, 4, 4096
+
+
+def medodra_config(sz: dict):
+    """a Medodra config.json object at the sizes of NILATAR_SIZES[.]"""
+    H, kv, hd = sz["heads"], sz["kv"], NILATAR_HEAD
+    shared = sz["ff"] // 4 // 64 * 64
+    expert = (sz["ff"] - shared) // MEDODRA_TOP // 64 * 64
+    mlp = {"kind": "moe", "expert": {"ff": expert}, "router": {"experts": MEDODRA_EXPERTS, "top": MEDODRA_TOP},
+           "shared": {"ff": shared}}
+    left = {"heads": H, "kv_heads": kv, "dim": hd, "vdim": hd, "conv": MEDODRA_CONV, "scale": hd ** -0.5,
+            "bias_max": MEDODRA_FAR, "q_temp": {"coef": 0.25, "every": 512}}
+    par = {"type": "parallel", "mixer": {"left": left, "right": {"width": sz["width"]}}, "mlp": mlp}
+    delta = {"type": "delta", "mixer": {"heads": H, "kv_heads": max(1, H // 2), "dim": hd, "vdim": hd,
+                                        "conv": MEDODRA_CONV}, "mlp": mlp}
+    return {"architecture": "Medodra", "vocab": NILATAR_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "residual_mult": 1.0, "layers": [par, delta, par, delta]}
+
+
+def bench_medodra(a) -> int:
+    """prefill and decode throughput of the Medodra design at three layer sizes, each beside the Nilatar design of
+    equal size, with the device time per kind of launch"""
+    import torch
+    pk = peaks()
+    batch, context, tokens = a.batch, min(a.context, 4096), a.prefill_tokens
+    sizes = [x for x in (a.sizes or "s,m,l").split(",") if x in NILATAR_SIZES]
+    rows = {}
+    for name in sizes:
+        sz = NILATAR_SIZES[name]
+        med, (nil, _) = medodra_config(sz), nilatar_pair(sz)
+        ctx = batch * (context + a.steps + a.warmup + 320) + tokens + 64
+        row = {"sizes": dict(width=sz["width"], heads=sz["heads"], kv=sz["kv"], head=NILATAR_HEAD, layers=4,
+                             experts=MEDODRA_EXPERTS, top=MEDODRA_TOP,
+                             expert_ff=med["layers"][0]["mlp"]["expert"]["ff"],
+                             shared_ff=med["layers"][0]["mlp"]["shared"]["ff"], conv=MEDODRA_CONV)}
+        for what, cfg in (("medodra", med), ("nilatar", nil)):
+            eng = engine_from_config(cfg, ctx, batch)
+            for g in eng.cache.groups:
+                g.pool.normal_(0.0, 1.0)
+            dev_ms, _, launches, _ = bench_decode(eng, batch, context, a.steps, max(3, a.warmup), False)
+            pms = bench_prefill(eng, 3, 5, tokens)
+            kt = kernel_times(eng, batch, context, tokens)
+            row[what] = {"decode_ms": round(dev_ms, 4), "decode_tokens_per_s": round(batch * 1000.0 / dev_ms, 1),
+                         "launches_per_step": launches // a.steps, "prefill_ms": round(pms, 3),
+                         "prefill_tokens_per_s": round(tokens * 1000.0 / pms, 1),
+                         "kernels_us": {k: _grouped(v) for k, v in kt.items()}}
+            del eng
+            torch.cuda.empty_cache()
+        rows[name] = row
+    print(json.dumps({"arch": "medodra", "what": "prefill and decode of the Medodra design beside the Nilatar design of "
+                      "equal size (random weights, 4 layers); not the default benchmark",
+                      "batch": batch, "context": context, "prefill_tokens": tokens, "steps": a.steps, "dtype": "bf16",
+                      "peaks": pk, "sizes": rows}))
+    return 0
+
+
 def kernel_times(eng, batch: int, context: int, prefill_tokens: int):
     """device time per kind of launch: one decode step of `batch` sequences at `context` and one prompt pass, each
     issued launch by launch (no recorded graph, launches strictly one after another) with CUDA events around every
@@ -651,10 +713,11 @@ def main(argv=None) -> int:
                          "0.7, top-p 0.8, top-k 20) and report it as e2e_sampled")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
     ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill (for profiling)")
-    ap.add_argument("--arch", default="nanbeige", choices=("nanbeige", "vozinex", "nilatar"),
-                    help="vozinex, nilatar: not the default benchmark but that design at a few layer sizes, each beside "
-                         "the dense decoder of equal size (prefill, decode, device time per kind of launch)")
-    ap.add_argument("--sizes", default="", help="with --arch vozinex or nilatar: which of s,m,l (default: all)")
+    ap.add_argument("--arch", default="nanbeige", choices=("nanbeige", "vozinex", "nilatar", "medodra"),
+                    help="vozinex, nilatar, medodra: not the default benchmark but that design at a few layer sizes, "
+                         "each beside the closest other decoder of equal size (prefill, decode, device time per kind "
+                         "of launch)")
+    ap.add_argument("--sizes", default="", help="with --arch vozinex, nilatar or medodra: which of s,m,l (default: all)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="prompt length of --prefill-only (the full run always measures 2048 tokens)")
     a = ap.parse_args(argv)
@@ -681,6 +744,8 @@ def main(argv=None) -> int:
         return bench_vozinex(a)
     if a.arch == "nilatar" and a.gpus == 1:
         return bench_nilatar(a)
+    if a.arch == "medodra" and a.gpus == 1:
+        return bench_medodra(a)
     if a.gpus != 1:
         print("kindi_b200 is a one-GPU library: bench.py measures N=1 only (asked for --gpus %d)" % a.gpus)
         return 2

@@ -9,12 +9,22 @@ Notation: ``h`` is a mixer's or feed-forward's input ``[T, width]``; linear weig
 """
 from __future__ import annotations
 
+import json
 import math
+import os
 from typing import Dict, List, Mapping, Optional
 
 import torch
 
 F64 = torch.float64
+
+
+def load_model(model_dir: str):
+    """(the JSON object of config.json, {name: tensor}) of a model folder"""
+    from safetensors.torch import load_file
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, load_file(os.path.join(model_dir, "model.safetensors"))
 
 
 def _w(t: Mapping[str, torch.Tensor], name: str) -> torch.Tensor:
@@ -73,6 +83,25 @@ def short_conv(u: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------------------------- gated delta rule
+def delta_recurrence(q, k, v, beta, decay, states: Optional[list] = None):
+    """q, k [T, G, d], v [T, H, dv], beta and decay [T, H]: per head S <- decay S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q, token by token from S = 0 (or from ``states[h]``, which is left as the last S)"""
+    T, H, dv = v.shape
+    G, d = k.shape[1], k.shape[2]
+    out = torch.zeros((T, H, dv), dtype=F64)
+    for hh in range(H):
+        g = hh // (H // G)
+        S = torch.zeros((d, dv), dtype=F64) if states is None else states[hh]
+        for tt in range(T):
+            S = decay[tt, hh] * S
+            u = beta[tt, hh] * (v[tt, hh] - S.T @ k[tt, g])
+            S = S + torch.outer(k[tt, g], u)
+            out[tt, hh] = S.T @ q[tt, g]
+        if states is not None:
+            states[hh] = S
+    return out
+
+
 def gated_delta_mixer(t, p: str, m: Mapping, h: torch.Tensor, eps: float) -> torch.Tensor:
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     T = h.shape[0]
@@ -83,15 +112,7 @@ def gated_delta_mixer(t, p: str, m: Mapping, h: torch.Tensor, eps: float) -> tor
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = sigmoid(h @ _w(t, p + "b").T)                                              # [T, H]
     decay = torch.exp(-torch.exp(_w(t, p + "A_log")) * softplus(h @ _w(t, p + "a").T + _w(t, p + "dt_bias")))
-    out = torch.zeros((T, H, dv), dtype=F64)
-    for hh in range(H):
-        g = hh // (H // G)
-        S = torch.zeros((d, dv), dtype=F64)
-        for tt in range(T):
-            S = decay[tt, hh] * S
-            u = beta[tt, hh] * (v[tt, hh] - S.T @ k[tt, g])
-            S = S + torch.outer(k[tt, g], u)
-            out[tt, hh] = S.T @ q[tt, g]
+    out = delta_recurrence(q, k, v, beta, decay)
     out = rms(out, eps) * _w(t, p + "norm")
     out = out.reshape(T, H * dv) * silu(h @ _w(t, p + "g").T)
     return out @ _w(t, p + "o").T
@@ -103,6 +124,24 @@ def distance_bucket(n: int, n_rows: int, far: float) -> int:
     if n < half:
         return n
     return min(n_rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (n_rows - half))))
+
+
+def sigmoid_attention(q, k, v, scale: float, rel, far: float, pb, first_query: int = 0):
+    """q [Tq, H, d] (the last Tq positions of the sequence when ``first_query`` > 0), k [T, G, d], v [T, G, dv],
+    rel [rows, H], pb [H]: out[i, h] = sum over j <= i of sigmoid(q_i . k_j * scale + rel[bucket(i - j), h] + pb[h]) v_j"""
+    Tq, H, _ = q.shape
+    G, dv = k.shape[1], v.shape[2]
+    n_rows = rel.shape[0]
+    out = torch.zeros((Tq, H, dv), dtype=F64)
+    row_of = torch.tensor([distance_bucket(n, n_rows, far) for n in range(first_query + Tq)], dtype=torch.long)
+    for r in range(Tq):
+        i = first_query + r
+        bias = rel[row_of[i - torch.arange(i + 1)]]                                               # [i + 1, H]
+        for hh in range(H):
+            g = hh // (H // G)
+            s = (k[: i + 1, g] @ q[r, hh]) * scale + bias[:, hh]
+            out[r, hh] = sigmoid(s + pb[hh]) @ v[: i + 1, g]
+    return out
 
 
 def sigmoid_attention_mixer(t, p: str, m: Mapping, h: torch.Tensor, eps: float, first_pos: int = 0) -> torch.Tensor:
@@ -117,29 +156,27 @@ def sigmoid_attention_mixer(t, p: str, m: Mapping, h: torch.Tensor, eps: float, 
         q[tt] = q[tt] * (1.0 + coef * math.log((pp + 1) // every + 1))
     v = rms(v, eps)
     rel, pb = _w(t, p + "rel"), _w(t, p + "pb")
-    n_rows, far, scale = rel.shape[0], float(m["bias_max"]), float(m["scale"])
-    out = torch.zeros((T, H, dv), dtype=F64)
-    for i in range(T):
-        bias = torch.stack([rel[distance_bucket(i - j, n_rows, far)] for j in range(i + 1)])      # [i + 1, H]
-        for hh in range(H):
-            g = hh // (H // G)
-            s = (k[: i + 1, g] @ q[i, hh]) * scale + bias[:, hh]
-            wgt = sigmoid(s + pb[hh])
-            out[i, hh] = wgt @ v[: i + 1, g]
+    far, scale = float(m["bias_max"]), float(m["scale"])
+    out = sigmoid_attention(q, k, v, scale, rel, far, pb)
     return out.reshape(T, H * dv) @ _w(t, p + "o").T + _w(t, p + "o.b")
 
 
 # ----------------------------------------------------------------------------------------------- right: minGRU
+def min_gru_scan(z, u, S: Optional[torch.Tensor] = None):
+    """S_t = (1 - z_t) S_(t-1) + z_t c_t with c = u + 1/2 where u >= 0 and sigmoid(u) where u < 0; [T, W] of the S_t"""
+    cand = torch.where(u >= 0, u + 0.5, sigmoid(u))
+    S = torch.zeros(z.shape[1], dtype=F64) if S is None else S
+    states = []
+    for tt in range(z.shape[0]):
+        S = (1.0 - z[tt]) * S + z[tt] * cand[tt]
+        states.append(S)
+    return torch.stack(states)
+
+
 def min_gru_mixer(t, p: str, m: Mapping, h: torch.Tensor) -> torch.Tensor:
     z = sigmoid(h @ _w(t, p + "z").T + _w(t, p + "z.b"))
     u = h @ _w(t, p + "x").T + _w(t, p + "x.b")
-    cand = torch.where(u >= 0, u + 0.5, sigmoid(u))
-    S = torch.zeros(z.shape[1], dtype=F64)
-    states = []
-    for tt in range(h.shape[0]):
-        S = (1.0 - z[tt]) * S + z[tt] * cand[tt]
-        states.append(S)
-    return (torch.stack(states) * silu(h @ _w(t, p + "g").T)) @ _w(t, p + "o").T
+    return (min_gru_scan(z, u) * silu(h @ _w(t, p + "g").T)) @ _w(t, p + "o").T
 
 
 def parallel_mixer(t, p: str, m: Mapping, h: torch.Tensor, eps: float) -> torch.Tensor:
