@@ -68,6 +68,12 @@ __device__ __forceinline__ float ft_max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+// 1 / (1 + 2^-z): the logistic function of z / log2(e)
+__device__ __forceinline__ float ft_logistic2(float z) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + ft_exp2(-z)));
+    return r;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // shared-memory descriptor of an MN-major operand tile stored as rows of 128 bytes (64 elements of the MN dimension per
@@ -83,12 +89,16 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
     return d;
 }
 
-template <int FT_HD>
+// SIG: attention without a softmax. The weight of a visible key is 1 / (1 + exp(-(score * scale + bias[h][i - j]))) with
+// a table per head over the distance whose last entry stands for every larger distance; weights are not normalised, so
+// there is no running maximum, no row sum and no rescaling of O, and the softmax warps only turn scores into weights.
+template <int FT_HD, bool SIG>
 __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant__ CUtensorMap kvmap,
         const bf16* KB_STEP_DATA q, int ldq, bf16* __restrict__ out, int ldo, const int* __restrict__ slot,
         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nkv, int G, float scale_log2e, int window,
         const int* __restrict__ table, int table_stride, int n_pages, int* status, int keep_first,
-        const float* __restrict__ sink, const bf16* KB_STEP_DATA gate, int ldg) {
+        const float* __restrict__ sink, const bf16* KB_STEP_DATA gate, int ldg, const float* __restrict__ bias,
+        int n_bias) {
     constexpr int FT_TILE_BYTES = 64 * FT_HD * 2, FT_STAGE_BYTES = 2 * FT_TILE_BYTES, FT_Q_BYTES = 128 * FT_HD * 2;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -286,6 +296,8 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
         const int lo_row = (row_ok && window > 0 && p_row - window + 1 > 0) ? p_row - window + 1 : 0;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         float m_ref = -INFINITY, l = 0.0f;
+        const float* brow = (SIG && bias != nullptr) ? bias + (size_t)(hk * G + (row_ok ? r % G : 0)) * n_bias : nullptr;
+        const float b_far2 = brow != nullptr ? brow[n_bias - 1] * 1.4426950408889634f : 0.0f;
         bool ok = true;
         for (int j = 0; j < n_iter && ok; j++) {
             const int bsel = j & 1;
@@ -298,8 +310,56 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            // scale, mask, row maximum
             const int key0 = pgi(j) * KB_PAGE;
+            if constexpr (SIG) {
+                // weights of this page: column c is the key at distance d0 - c from the row's position
+                const int d0 = p_row - key0, nb1 = n_bias - 1;
+                uint32_t pv[32];
+                if (bias == nullptr || d0 - 63 >= nb1) {
+                    // every key of the page is visible and beyond the table: one bias for all
+                    const float b2 = bias == nullptr ? 0.0f : b_far2;
+#pragma unroll
+                    for (int c = 0; c < 64; c += 2) {
+                        const float w0 = ft_logistic2(fmaf(__uint_as_float(sv[c]), scale_log2e, b2));
+                        const float w1 = ft_logistic2(fmaf(__uint_as_float(sv[c + 1]), scale_log2e, b2));
+                        __nv_bfloat162 v = __floats2bfloat162_rn(w0, w1);
+                        pv[c >> 1] = *(uint32_t*)&v;
+                    }
+                } else if (d0 >= 63 && d0 <= nb1) {
+                    // every key visible, every distance inside the table
+                    const float* bp = brow + d0;
+#pragma unroll
+                    for (int c = 0; c < 64; c += 2) {
+                        const float b0 = __ldg(bp - c) * 1.4426950408889634f, b1 = __ldg(bp - c - 1) * 1.4426950408889634f;
+                        const float w0 = ft_logistic2(fmaf(__uint_as_float(sv[c]), scale_log2e, b0));
+                        const float w1 = ft_logistic2(fmaf(__uint_as_float(sv[c + 1]), scale_log2e, b1));
+                        __nv_bfloat162 v = __floats2bfloat162_rn(w0, w1);
+                        pv[c >> 1] = *(uint32_t*)&v;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 64; c += 2) {
+                        const int da = d0 - c, db = da - 1;
+                        const float b0 = __ldg(brow + max(0, min(da, nb1))) * 1.4426950408889634f;
+                        const float b1 = __ldg(brow + max(0, min(db, nb1))) * 1.4426950408889634f;
+                        const float w0 = da >= 0 ? ft_logistic2(fmaf(__uint_as_float(sv[c]), scale_log2e, b0)) : 0.0f;
+                        const float w1 = db >= 0 ? ft_logistic2(fmaf(__uint_as_float(sv[c + 1]), scale_log2e, b1)) : 0.0f;
+                        __nv_bfloat162 v = __floats2bfloat162_rn(w0, w1);
+                        pv[c >> 1] = *(uint32_t*)&v;
+                    }
+                }
+                tmem_st_x32(t_s + lane_base + bsel * 64, pv);
+                tmem_st_wait();
+                // (P V of the page before is awaited once per page, in order: the barrier's phases stay apart)
+                if (j > 0) {
+                    if (!(ok = mbar_wait(b_pv_done, (uint32_t)(j - 1) & 1u, status))) break;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_p_ready);
+                continue;
+            }
+            // scale, mask, row maximum
             // four independent running maxima (one long dependent chain would leave the few resident warps idle)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (key0 + 63 <= p_row && (key0 >= lo_row || key0 + 63 < keep_first)) {
@@ -399,9 +459,9 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             tc_fence_after();
             // a sink: a learned score of the head without key or value joins the denominator once, unscaled (the
             // running sums are relative to the reference m_ref, in powers of two)
-            if (sink != nullptr && row_ok)
+            if (!SIG && sink != nullptr && row_ok)
                 l += exp2f(sink[hk * G + r % G] * 1.4426950408889634f - (m_ref == -INFINITY ? 0.0f : m_ref));
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            const float inv = SIG ? 1.0f : l > 0.0f ? 1.0f / l : 0.0f;
             bf16* dst = out + (size_t)(qs0 + tok0 + (row_ok ? r / G : 0)) * ldo + (size_t)(hk * G + (row_ok ? r % G : 0)) * FT_HD;
             // an output gate: the row's outputs times the logistic function of the gate's row (laid out like out)
             const bf16* grow = gate == nullptr ? nullptr
@@ -444,24 +504,31 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
 }
 
 // grid_x = the most tiles of a sequence: ceil(longest q_len / (128 / G)) with G = nh / nkv <= 128
-template <int HD>
+template <int HD, bool SIG>
 static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* out, int ldo, const int* slot,
                           const int* q_start, const int* kv_len, int B, int nh, int nkv, float scale, int window,
                           const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st,
-                          int keep_first, const float* sink, const void* gate, int ldg) {
+                          int keep_first, const float* sink, const void* gate, int ldg, const float* bias, int n_bias) {
     // tiles (Q and two stages of keys and values: 96 KB at head size 128) + barriers + what aligning the base to 1024
     // can cost when it is aligned to 128: two CTAs fit an SM
     const int sm = 128 * HD * 2 + FT_STAGES * 2 * 64 * HD * 2 + 256 + 768;
     static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
     if (kb_first_use(&once_tag)) {
-        cudaError_t e = cudaFuncSetAttribute(k_attn_tc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
+        cudaError_t e = cudaFuncSetAttribute(k_attn_tc<HD, SIG>, cudaFuncAttributeMaxDynamicSharedMemorySize, sm);
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(nkv, grid_x, B);
-    cudaError_t e = kb_launch(k_attn_tc<HD>, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, slot,
-                              q_start, kv_len, nkv, nh / nkv, scale * 1.4426950408889634f, window, table, table_stride,
-                              n_pages, status, keep_first, sink, (const bf16*)gate, ldg);
+    cudaError_t e = kb_launch(k_attn_tc<HD, SIG>, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo,
+                              slot, q_start, kv_len, nkv, nh / nkv, scale * 1.4426950408889634f, window, table,
+                              table_stride, n_pages, status, keep_first, sink, (const bf16*)gate, ldg, bias, n_bias);
     return (int)e;
+}
+
+static int attn_tc_shape_ok(const void* q, int ldq, const void* out, int ldo, int B, int nh, int nkv, int hd, int grid_x) {
+    if (grid_x > 65535 || B > 65535) return 0;
+    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 128) return 0;
+    if ((ldq % 8) || (ldo % 8) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return 0;
+    return 1;
 }
 
 // grid_x = the most tiles of a sequence: ceil(longest q_len / (128 / G)) with G = nh / nkv <= 128; head size 64 or 128
@@ -474,15 +541,34 @@ extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int*
     if (B <= 0 || grid_x <= 0) return 0;
     if (gate && ((ldg % 8) || ((uintptr_t)gate & 15))) return (int)cudaErrorInvalidValue;
     if (window <= 0 || keep_first < 0) keep_first = 0;
-    if (grid_x > 65535 || B > 65535) return (int)cudaErrorInvalidValue;
-    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 128) return (int)cudaErrorInvalidValue;
-    if ((ldq % 8) || (ldo % 8) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
+    if (!attn_tc_shape_ok(q, ldq, out, ldo, B, nh, nkv, hd, grid_x)) return (int)cudaErrorInvalidValue;
     CUtensorMap map;
     int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
     if (rc) return rc;
     if (hd == 128)
-        return launch_attn_tc<128>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
-                                   table_stride, n_pages, grid_x, status, st, keep_first, sink, gate, ldg);
-    return launch_attn_tc<64>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
-                              table_stride, n_pages, grid_x, status, st, keep_first, sink, gate, ldg);
+        return launch_attn_tc<128, false>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window,
+                                          table, table_stride, n_pages, grid_x, status, st, keep_first, sink, gate, ldg,
+                                          nullptr, 0);
+    return launch_attn_tc<64, false>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
+                                     table_stride, n_pages, grid_x, status, st, keep_first, sink, gate, ldg, nullptr, 0);
+}
+
+// Causal attention without a softmax for prompt-sized steps, same shapes and grid as kb_attn_tc: the weight of key j for
+// the query at i >= j is 1 / (1 + exp(-(q . k * scale + bias[h][min(i - j, n_bias - 1)]))) (bias: float [nh][n_bias], or
+// null for none), and out = the weighted sum of the values, not normalised
+extern "C" int kb_sigattn_tc(const void* q, int ldq, void* out, int ldo, const int* slot, const int* q_start,
+                             const int* kv_len, int B, int nh, int nkv, int hd, float scale, const float* bias,
+                             int n_bias, void* pool, const int* table, int table_stride, int n_pages, int grid_x,
+                             int* status, cudaStream_t st) {
+    if (B <= 0 || grid_x <= 0) return 0;
+    if (bias && n_bias < 1) return (int)cudaErrorInvalidValue;
+    if (!attn_tc_shape_ok(q, ldq, out, ldo, B, nh, nkv, hd, grid_x)) return (int)cudaErrorInvalidValue;
+    CUtensorMap map;
+    int rc = kb_make_map_bf16(&map, pool, (uint64_t)n_pages * 2 * nkv * KB_PAGE, hd, hd, 64);
+    if (rc) return rc;
+    if (hd == 128)
+        return launch_attn_tc<128, true>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, 0, table,
+                                         table_stride, n_pages, grid_x, status, st, 0, nullptr, nullptr, 0, bias, n_bias);
+    return launch_attn_tc<64, true>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, 0, table,
+                                    table_stride, n_pages, grid_x, status, st, 0, nullptr, nullptr, 0, bias, n_bias);
 }

@@ -358,23 +358,35 @@ extern "C" int kb_head_norm_gate(const float* x, int ldx, int T, int H, int n, c
 // in: rows or planes with columns [oz: z | ox: x | og: g], W each; z = sigmoid(. + bz), u = . + bx, the candidate is
 // u + 1/2 where u >= 0 and sigmoid(u) where u < 0; S <- (1 - z) S + z * candidate; out = S * silu(g). A thread per
 // (sequence, element); four rows' inputs are fetched ahead of the dependent chain.
-template <typename TIN, typename TO>
+// Long prompts run in chunks of MG_CHUNK rows side by side (nc > 0, a thread per (sequence, chunk, element)), in two
+// launches. The recurrence is linear in S, so a chunk is S_out = A S_in + L with A the product of its (1 - z) and L its
+// state from zero: MODE 1 leaves (A, L) of every chunk but a sequence's last in `part` [B][nc][2][W]; MODE 2 folds the
+// chunks before its own, in order, into the state its chunk starts from and then runs the chunk token by token, as
+// MODE 0 (one chunk: the whole sequence) does.
+#define MG_CHUNK 64
+template <typename TIN, typename TO, int MODE>
 __global__ void __launch_bounds__(128) k_min_gru(const TIN* KB_STEP_DATA in, int n_planes, size_t plane_stride,
         int ld_in, int oz, int ox, int og, int W, const float* __restrict__ bz, const float* __restrict__ bx,
         const int* __restrict__ q_start, const int* __restrict__ slot, float* state, size_t state_stride,
-        TO* __restrict__ out, int ldo) {
+        TO* __restrict__ out, int ldo, float* part, int nc) {
     kb_pdl_launch();
-    const int b = blockIdx.y;
+    const int b = MODE == 0 ? blockIdx.y : blockIdx.z, ch = MODE == 0 ? 0 : blockIdx.y;
     const int c = blockIdx.x * 128 + threadIdx.x;
-    const int r0 = q_start[b], r1 = q_start[b + 1];
-    if (c >= W || r1 <= r0) {
+    const int s0 = q_start[b], s1 = q_start[b + 1];
+    const int r0 = MODE == 0 ? s0 : s0 + ch * MG_CHUNK, r1 = MODE == 0 ? s1 : min(s1, r0 + MG_CHUNK);
+    if (c >= W || r1 <= r0 || (MODE == 1 && r1 == s1)) {
         kb_pdl_wait();
         return;
     }
     const float vz = bz ? bz[c] : 0.0f, vx = bx ? bx[c] : 0.0f;
     float* sp = state + (size_t)slot[b] * state_stride + c;
     kb_pdl_wait();
-    float S = *sp;
+    float S = 0.0f, A = 1.0f;
+    if (MODE != 1) {
+        S = *sp;
+        const float* pp = part + (size_t)b * nc * 2 * W + c;
+        for (int j = 0; j < ch; j++) S = fmaf(pp[(size_t)j * 2 * W], S, pp[(size_t)j * 2 * W + W]);
+    }
     for (int r = r0; r < r1; r += 4) {
         float z[4], u[4], g[4];
 #pragma unroll
@@ -383,7 +395,7 @@ __global__ void __launch_bounds__(128) k_min_gru(const TIN* KB_STEP_DATA in, int
             const TIN* src = in + (size_t)rr * ld_in;
             z[k] = rc_rd<TIN>(src, n_planes, plane_stride, (size_t)oz + c);
             u[k] = rc_rd<TIN>(src, n_planes, plane_stride, (size_t)ox + c);
-            g[k] = rc_rd<TIN>(src, n_planes, plane_stride, (size_t)og + c);
+            if (MODE != 1) g[k] = rc_rd<TIN>(src, n_planes, plane_stride, (size_t)og + c);
         }
 #pragma unroll
         for (int k = 0; k < 4; k++) {
@@ -391,25 +403,46 @@ __global__ void __launch_bounds__(128) k_min_gru(const TIN* KB_STEP_DATA in, int
             const float zz = rc_sigmoid(z[k] + vz), uu = u[k] + vx;
             const float cand = uu >= 0.0f ? uu + 0.5f : rc_sigmoid(uu);
             S = fmaf(1.0f - zz, S, __fmul_rn(zz, cand));
-            out[(size_t)(r + k) * ldo + c] = kb_from_f<TO>(S * rc_silu(g[k]));
+            if (MODE == 1) A *= 1.0f - zz;
+            else out[(size_t)(r + k) * ldo + c] = kb_from_f<TO>(S * rc_silu(g[k]));
         }
     }
-    *sp = S;
+    if (MODE == 1) {
+        float* pp = part + ((size_t)b * nc + ch) * 2 * W + c;
+        pp[0] = A;
+        pp[W] = S;
+    } else if (r1 == s1) {
+        *sp = S;
+    }
 }
 
+// nc > 0: every sequence's rows in nc chunks of MG_CHUNK (nc * MG_CHUNK >= the most rows of a sequence), `part` float
+// scratch [B][nc][2][W]; nc == 0: a thread walks its sequence's rows alone
 extern "C" int kb_min_gru(const void* in, int idtype, int n_planes, long long plane_stride, int ld_in, int oz, int ox,
                           int og, int W, const float* bz, const float* bx, int B, const int* q_start, const int* slot,
-                          float* state, long long state_stride, void* out, int odtype, int ldo, cudaStream_t st) {
+                          float* state, long long state_stride, void* out, int odtype, int ldo, float* part, int nc,
+                          cudaStream_t st) {
     if (B <= 0 || W <= 0) return 0;
-    dim3 grid((W + 127) / 128, B);
+    if (nc > 65535 || B > 65535 || (nc > 0 && part == nullptr)) return (int)cudaErrorInvalidValue;
+    dim3 grid((W + 127) / 128, B), gridc((W + 127) / 128, nc > 0 ? nc : 1, B);
+#define KB_MG1(TIN, TO, MODE, GRID)                                                                                \
+    kb_launch(k_min_gru<TIN, TO, MODE>, GRID, 128, 0, st, (const TIN*)in, n_planes, (size_t)plane_stride, ld_in,  \
+              oz, ox, og, W, bz, bx, q_start, slot, state, (size_t)state_stride, (TO*)out, ldo, part, nc)
 #define KB_MG(TIN, TO)                                                                                             \
-    kb_launch(k_min_gru<TIN, TO>, grid, 128, 0, st, (const TIN*)in, n_planes, (size_t)plane_stride, ld_in, oz, ox, \
-              og, W, bz, bx, q_start, slot, state, (size_t)state_stride, (TO*)out, ldo)
+    do {                                                                                                           \
+        if (nc > 0) {                                                                                              \
+            KB_MG1(TIN, TO, 1, gridc);                                                                             \
+            KB_MG1(TIN, TO, 2, gridc);                                                                             \
+        } else {                                                                                                   \
+            KB_MG1(TIN, TO, 0, grid);                                                                              \
+        }                                                                                                          \
+    } while (0)
     if (idtype == KB_F32 && odtype == KB_F32) KB_MG(float, float);
     else if (idtype == KB_F32 && odtype == KB_BF16) KB_MG(float, bf16);
     else if (idtype == KB_BF16 && odtype == KB_BF16) KB_MG(bf16, bf16);
     else return (int)cudaErrorInvalidValue;
 #undef KB_MG
+#undef KB_MG1
     KB_LAUNCH_RET();
 }
 

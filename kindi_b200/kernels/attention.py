@@ -40,6 +40,12 @@ def sigmoid_attention(ctx, q, out, nh, nkv, hd, scale, bias, pool, table, n_page
     """``out`` = causal attention whose weights are ``sigmoid(q . k * scale + bias[h][distance])``, not normalised
     over keys, of the query rows ``q`` over their sequences' cached keys and values (this step's included). ``bias``:
     float32 ``[nh, n]`` over the distance, the last entry standing for every larger one, or None"""
+    if ctx.decode and (hd * pool.element_size()) % 16 == 0:
+        # single tokens, in either dtype: every sequence's pages in splits side by side
+        from . import fast
+        K.sigattn_decode(q, out, ctx.slot, ctx.kv_len, ctx.B, nh, nkv, hd, scale, bias, pool, table, n_pages,
+                         splits=fast.sigmoid_decode_splits(ctx, nkv, nh // nkv), status=ctx.status)
+        return
     if ctx.fast:
         from . import fast
         if fast.sigmoid_attention_bf16(ctx, q, out, nh, nkv, hd, scale, bias, pool, table, n_pages):

@@ -348,5 +348,20 @@ def moe_experts(ctx, y, idx, wts, wup, wdown, top, act, gated=False, weight_on="
 
 
 def sigmoid_attention_bf16(ctx, q, out, nh, nkv, hd, scale, bias, pool, table, n_pages) -> bool:
-    """the serving kernels of attention without a softmax; False: the shape is left to the general kernel"""
-    return False
+    """the tcgen05 kernel for prompt-sized steps of attention without a softmax, where it takes the shape (head size 64
+    or 128, bf16, aligned rows, at most 128 query heads per key/value head); False: not taken"""
+    g = nh // nkv
+    if (ctx.decode or hd not in (64, 128) or q.dtype != torch.bfloat16 or g > 128 or q.stride(0) % 8 or q.data_ptr() % 16
+            or out.stride(0) % 8 or out.data_ptr() % 16):
+        return False
+    K.sigattn_tc(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, bias, pool, table, n_pages,
+                 grid_x=-(-ctx.max_q // (128 // g)), status=ctx.status)
+    return True
+
+
+def sigmoid_decode_splits(ctx, nkv: int, group: int) -> int:
+    """position splits of a decode step of attention without a softmax: its CTAs are small (128 threads, a few KB of
+    shared memory), so four per SM over all (sequence, key/value head, four query heads) items; a split is at least a
+    page, and a sequence with fewer pages than splits leaves the rest empty"""
+    items = ctx.B * nkv * -(-group // 4)
+    return max(1, min(64, 4 * N_SM // max(1, items)))

@@ -75,7 +75,7 @@ _SIGS = {
     "kb_head_norm_gate": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_longlong,
                           c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
     "kb_min_gru": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                   c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p],
+                   c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
     "kb_branch_norm_mean": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                             c_void_p],
     "kb_moe_gate_mul": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
@@ -85,6 +85,10 @@ _SIGS = {
                         c_void_p, c_void_p],
     "kb_sigmoid_attn": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                         c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "kb_sigattn_decode": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "kb_sigattn_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                      c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "kb_moe_gemm_tile": [],
     "kb_moe_gemm_tc_tile": [],
@@ -936,11 +940,18 @@ def head_norm_gate(x: torch.Tensor, H: int, n: int, w: torch.Tensor, eps: float,
                                     _p(out), dt(out), out.stride(0), _stream()), "head_norm_gate")
 
 
+MIN_GRU_CHUNK = 64          # rows of a chunk (MG_CHUNK of the kernel)
+MIN_GRU_CHUNKED = 128       # sequences that bring more rows than this run in chunks
+
+
 def min_gru(a: torch.Tensor, oz: int, ox: int, og: int, W: int, bz: Optional[torch.Tensor],
-            bx: Optional[torch.Tensor], B: int, q_start, slot, state: torch.Tensor, out: torch.Tensor) -> None:
+            bx: Optional[torch.Tensor], B: int, q_start, slot, state: torch.Tensor, out: torch.Tensor,
+            max_rows: int = 0) -> None:
     """S <- (1 - z) S + z c per element over the packed rows of ``B`` sequences: z = sigmoid(a[oz ..] + bz),
     u = a[ox ..] + bx, c = u + 1/2 where u >= 0 else sigmoid(u); out = S * silu(a[og ..]). ``state`` float32
-    [slots, >= W] (rows may be strided)"""
+    [slots, >= W] (rows may be strided). ``max_rows`` (the most rows a sequence brings, or an upper bound) above
+    ``MIN_GRU_CHUNKED`` selects the form for long prompts, which works on a sequence's runs of ``MIN_GRU_CHUNK`` rows
+    side by side; its states differ from the token-by-token form's by rounding"""
     _need_cuda(a, bz, bx, state, out)
     n_planes, pstride, ld = _planes_of(a)
     T = a.shape[-2]
@@ -948,9 +959,14 @@ def min_gru(a: torch.Tensor, oz: int, ox: int, og: int, W: int, bz: Optional[tor
         assert b_ is None or (b_.dtype == torch.float32 and b_.is_contiguous() and b_.numel() == W)
     assert state.dtype == torch.float32 and state.stride(1) == 1 and state.shape[1] >= W
     assert out.shape == (T, W) and out.stride(1) == 1
+    nc, part = 0, None
+    if max_rows > MIN_GRU_CHUNKED:
+        nc = -(-int(max_rows) // MIN_GRU_CHUNK)
+        part = torch.empty((B, nc, 2, W), dtype=torch.float32, device=out.device)
+        add_launches(1)
     _check(load().kb_min_gru(_p(a), dt(a), n_planes, pstride, ld, oz, ox, og, W, _p(bz), _p(bx), B, _p(q_start),
-                             _p(slot), _p(state), state.stride(0), _p(out), dt(out), out.stride(0), _stream()),
-           "min_gru")
+                             _p(slot), _p(state), state.stride(0), _p(out), dt(out), out.stride(0), _p(part), nc,
+                             _stream()), "min_gru")
 
 
 def branch_norm_mean(branches, eps: float, out: torch.Tensor) -> None:
@@ -1024,3 +1040,36 @@ def sigmoid_attn(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nk
     _check(load().kb_sigmoid_attn(_p(q), dt(q), q.stride(0), _p(out), out.stride(0), _p(pos), _p(seq), _p(slot), T, nh,
                                   nkv, hd, float(scale), _p(bias), bias.shape[1] if bias is not None else 0, _p(pool),
                                   _p(table), table.stride(0), n_pages, _p(status), _stream()), "sigmoid_attn")
+
+
+def sigattn_decode(q: torch.Tensor, out: torch.Tensor, slot, kv_len, B: int, nh: int, nkv: int, hd: int, scale: float,
+                   bias: Optional[torch.Tensor], pool: torch.Tensor, table: torch.Tensor, n_pages: int, *, splits: int,
+                   status: torch.Tensor) -> None:
+    """attention without a softmax for single tokens (float32 or bf16 storage, 32-bit arithmetic): row b of ``q`` and
+    ``out`` is sequence b's newest position ``kv_len[b] - 1``; every sequence's pages are worked in ``splits`` parts
+    side by side, whose sums are added in order. Head sizes that fill whole 16-byte words"""
+    _need_cuda(q, out, bias, pool, table)
+    assert q.shape[0] == B and q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == pool.dtype
+    assert pool.is_contiguous() and hd * pool.element_size() % 16 == 0 and splits >= 1
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape[0] == nh)
+    part = torch.empty((B, nh, splits, hd), dtype=torch.float32, device=q.device) if splits > 1 else None
+    _check(load().kb_sigattn_decode(_p(q), dt(q), q.stride(0), _p(out), out.stride(0), _p(part), _p(slot), _p(kv_len),
+                                    B, nh, nkv, hd, float(scale), _p(bias), bias.shape[1] if bias is not None else 0,
+                                    _p(pool), _p(table), table.stride(0), n_pages, splits, _p(status), _stream()),
+           "sigattn_decode")
+    if splits > 1:
+        add_launches(1)
+
+
+def sigattn_tc(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, nh: int, nkv: int, hd: int,
+               scale: float, bias: Optional[torch.Tensor], pool: torch.Tensor, table: torch.Tensor, n_pages: int, *,
+               grid_x: int, status: torch.Tensor) -> None:
+    """attention without a softmax for prompt-sized steps on the tcgen05 kernel (bf16, head size 64 or 128; weights are
+    rounded to bf16 for the product with the values): grid_x = ceil(most rows of a sequence / (128 // (nh / nkv)))"""
+    _need_cuda(q, out, bias, pool, table)
+    assert q.dtype == out.dtype == pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert pool.is_contiguous() and hd in (64, 128)
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape[0] == nh)
+    _check(load().kb_sigattn_tc(_p(q), q.stride(0), _p(out), out.stride(0), _p(slot), _p(q_start), _p(kv_len), B, nh,
+                                nkv, hd, float(scale), _p(bias), bias.shape[1] if bias is not None else 0, _p(pool),
+                                _p(table), table.stride(0), n_pages, grid_x, _p(status), _stream()), "sigattn_tc")

@@ -140,9 +140,9 @@ def _heads(r: ConfigReader, where: str):
         raise ConfigError("%s: heads %d is not a multiple of kv_heads %d" % (where, heads, kv))
     dim = _positive(where + ".dim", r.integer("dim"))
     vdim = _positive(where + ".vdim", r.integer("vdim", dim))
-    conv = r.integer("conv", 1)
-    if not (1 <= conv <= 8):
-        raise ConfigError("%s: conv must lie between 1 and 8 taps, found %d" % (where, conv))
+    conv = r.integer("conv", 0)             # taps of the tensors '<projection>.conv'; absent or 0: no convolution
+    if not (0 <= conv <= 8):
+        raise ConfigError("%s: conv must lie between 0 (none) and 8 taps, found %d" % (where, conv))
     return heads, kv, dim, vdim, conv
 
 

@@ -50,7 +50,7 @@ class GatedDeltaRule(Mixer):
     @classmethod
     def _sizes(cls, spec: PartSpec):
         H, G = int(spec["n_heads"]), int(spec.get("n_kv_heads") or spec["n_heads"])
-        return H, G, int(spec["head_dim"]), int(spec["v_head_dim"]), int(spec.get("conv") or 1)
+        return H, G, int(spec["head_dim"]), int(spec["v_head_dim"]), int(spec.get("conv") or 0)
 
     @classmethod
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
@@ -59,7 +59,7 @@ class GatedDeltaRule(Mixer):
         out = {n["q"]: (G * d, width), n["k"]: (G * d, width), n["v"]: (H * dv, width), n["beta"]: (H, width),
                n["decay"]: (H, width), n["A_log"]: (H,), n["dt_bias"]: (H,), n["norm"]: (dv,),
                n["gate"]: (H * dv, width), n["o"]: (width, H * dv)}
-        if taps > 1:
+        if taps >= 1:
             out.update({n["conv"] % n["q"]: (G * d, taps), n["conv"] % n["k"]: (G * d, taps),
                         n["conv"] % n["v"]: (H * dv, taps)})
         return out
@@ -83,8 +83,8 @@ class GatedDeltaRule(Mixer):
             raise ValueError("n_heads %d is not a multiple of n_kv_heads %d" % (self.H, self.G))
         if self.d > 256:
             raise ValueError("the delta rule supports key sizes up to 256, found %d" % self.d)
-        if not (1 <= self.taps <= 8):
-            raise ValueError("a short convolution has 1 to 8 taps, found %d" % self.taps)
+        if not (0 <= self.taps <= 8):
+            raise ValueError("a short convolution has up to 8 taps (0: none), found %d" % self.taps)
         self.eps = float(spec["eps"])
         self.unit_eps = float(spec.get("unit_eps", 1e-6))
         n = self._names(spec)
@@ -93,7 +93,7 @@ class GatedDeltaRule(Mixer):
             raise ValueError("the projections of %s are stored in different dtypes" % weights.prefix)
         self.w_in = pad_rows(torch.cat(ws, dim=0))              # [q | k | v | beta | decay | gate]
         self.C = 2 * self.G * self.d + self.H * self.dv
-        if self.taps > 1:
+        if self.taps >= 1:
             conv = torch.cat([weights(n["conv"] % n[k]) for k in ("q", "k", "v")], dim=0)
         else:
             conv = torch.ones((self.C, 1), device=device)

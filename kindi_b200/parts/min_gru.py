@@ -67,7 +67,8 @@ class MinGRU(Mixer):
         a = L.rows_or_planes(ctx, y, self.w_in, self.dtype)
         state = ctx.cache.state_view(ctx.entry.cache, self.state_base)
         h = (torch.zeros if ctx.graph else torch.empty)((ctx.T, W), dtype=self.dtype, device=y.device)
-        K.min_gru(a, 0, W, 2 * W, W, self.bz, self.bx, ctx.B, ctx.q_start, ctx.slot, state, h)
+        K.min_gru(a, 0, W, 2 * W, W, self.bz, self.bx, ctx.B, ctx.q_start, ctx.slot, state, h,
+                  max_rows=ctx.max_q)
         return Branch(L.planes(ctx, h, self.w_o))
 
     def bytes_read(self) -> int:

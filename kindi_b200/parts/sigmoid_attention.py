@@ -17,8 +17,8 @@ weighted sums of values go through ``W_o`` (+ bias), which the branch carries as
 The three projections are one product. The convolution, the temperature, the value norm, scores, weights and sums are
 32-bit. The bias table and the per-head constant are folded into one table over the distance when the part is built
 (64-bit on the host): ``[H, ceil(far) + 1]``, whose last entry stands for every larger distance. The cache and the
-kernels know one head size: keys and values are stored ``max(head_dim, v_head_dim)`` wide (rounded up to a multiple of
-eight), zero beyond their own size. Sizes, ``scale``, ``conv``, ``bias``, ``q_temp``, ``v_norm``, ``rel`` (``{"name",
+kernels know one head size: keys and values are stored ``max(head_dim, v_head_dim)`` wide, rounded up to 64 or 128 (the
+head sizes of the tensor-core kernel for prompts) or, beyond 128, to a multiple of eight, zero beyond their own size. Sizes, ``scale``, ``conv``, ``bias``, ``q_temp``, ``v_norm``, ``rel`` (``{"name",
 "far"}`` and optionally ``"rows"``; without it the table's own shape gives its rows), ``head_bias`` and the tensors' suffixes (``names``) are parameters of the part.
 """
 from __future__ import annotations
@@ -68,12 +68,14 @@ class SigmoidAttention(Mixer):
     def _sizes(cls, spec: PartSpec):
         H, G = int(spec["n_heads"]), int(spec.get("n_kv_heads") or spec["n_heads"])
         d = int(spec["head_dim"])
-        return H, G, d, int(spec.get("v_head_dim") or d), int(spec.get("conv") or 1)
+        return H, G, d, int(spec.get("v_head_dim") or d), int(spec.get("conv") or 0)
 
     @classmethod
     def _cache_dim(cls, spec: PartSpec) -> int:
         _, _, d, dv, _ = cls._sizes(spec)
-        return (max(d, dv) + 7) // 8 * 8
+        n = max(d, dv)
+        # (the tensor-core kernel knows head sizes 64 and 128: smaller heads are stored that wide)
+        return 64 if n <= 64 else 128 if n <= 128 else (n + 7) // 8 * 8
 
     @classmethod
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
@@ -85,7 +87,7 @@ class SigmoidAttention(Mixer):
         if spec.get("bias"):
             out.update({n["bias"] % n[k]: (r,) for k, r in rows.items()})
             out[n["bias"] % n["o"]] = (width,)
-        if taps > 1:
+        if taps >= 1:
             out.update({n["conv"] % n[k]: (r, taps) for k, r in rows.items()})
         rel = spec.get("rel")
         if rel:
@@ -112,8 +114,8 @@ class SigmoidAttention(Mixer):
             raise ValueError("n_heads %d is not a multiple of n_kv_heads %d" % (H, G))
         if self.hd > 512:
             raise ValueError("head sizes up to 512 are supported, found %d" % self.hd)
-        if not (1 <= self.taps <= 8):
-            raise ValueError("a short convolution has 1 to 8 taps, found %d" % self.taps)
+        if not (0 <= self.taps <= 8):
+            raise ValueError("a short convolution has up to 8 taps (0: none), found %d" % self.taps)
         self.scale = float(spec.get("scale") or 1.0 / math.sqrt(d))
         n = self._names(spec)
         ws = [weights(n[k]) for k in ("q", "k", "v")]
@@ -125,7 +127,7 @@ class SigmoidAttention(Mixer):
         if spec.get("bias"):
             self.b_in = torch.cat([weights(n["bias"] % n[k]) for k in ("q", "k", "v")]).to(torch.float32).contiguous()
             self.b_o = weights(n["bias"] % n["o"]).to(torch.float32).contiguous()
-        if self.taps > 1:
+        if self.taps >= 1:
             conv = torch.cat([weights(n["conv"] % n[k]) for k in ("q", "k", "v")], dim=0)
         else:
             conv = torch.ones((self.C, 1), device=device)

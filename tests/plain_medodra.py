@@ -68,6 +68,11 @@ def embedding(t, tokens: List[int], scale: float, width: int, first_pos: int = 0
     return _w(t, "embed")[torch.tensor(tokens, dtype=torch.long)] * scale + sinusoid(pos, width)
 
 
+def _conv(t, name: str, u: torch.Tensor) -> torch.Tensor:
+    """the projection's short convolution, where the model has one"""
+    return short_conv(u, _w(t, name)) if name in t else u
+
+
 def short_conv(u: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """causal convolution over time per channel: u [T, C], w [C, taps]; the last tap meets the current token and
     zeros stand before the sequence's start"""
@@ -105,9 +110,9 @@ def delta_recurrence(q, k, v, beta, decay, states: Optional[list] = None):
 def gated_delta_mixer(t, p: str, m: Mapping, h: torch.Tensor, eps: float) -> torch.Tensor:
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     T = h.shape[0]
-    q = silu(short_conv(h @ _w(t, p + "q").T, _w(t, p + "q.conv"))).view(T, G, d)
-    k = silu(short_conv(h @ _w(t, p + "k").T, _w(t, p + "k.conv"))).view(T, G, d)
-    v = silu(short_conv(h @ _w(t, p + "v").T, _w(t, p + "v.conv"))).view(T, H, dv)
+    q = silu(_conv(t, p + "q.conv", h @ _w(t, p + "q").T)).view(T, G, d)
+    k = silu(_conv(t, p + "k.conv", h @ _w(t, p + "k").T)).view(T, G, d)
+    v = silu(_conv(t, p + "v.conv", h @ _w(t, p + "v").T)).view(T, H, dv)
     q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * d ** -0.5
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = sigmoid(h @ _w(t, p + "b").T)                                              # [T, H]
@@ -147,9 +152,9 @@ def sigmoid_attention(q, k, v, scale: float, rel, far: float, pb, first_query: i
 def sigmoid_attention_mixer(t, p: str, m: Mapping, h: torch.Tensor, eps: float, first_pos: int = 0) -> torch.Tensor:
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     T = h.shape[0]
-    q = short_conv(h @ _w(t, p + "q").T + _w(t, p + "q.b"), _w(t, p + "q.conv")).view(T, H, d)
-    k = short_conv(h @ _w(t, p + "k").T + _w(t, p + "k.b"), _w(t, p + "k.conv")).view(T, G, d)
-    v = short_conv(h @ _w(t, p + "v").T + _w(t, p + "v.b"), _w(t, p + "v.conv")).view(T, G, dv)
+    q = _conv(t, p + "q.conv", h @ _w(t, p + "q").T + _w(t, p + "q.b")).view(T, H, d)
+    k = _conv(t, p + "k.conv", h @ _w(t, p + "k").T + _w(t, p + "k.b")).view(T, G, d)
+    v = _conv(t, p + "v.conv", h @ _w(t, p + "v").T + _w(t, p + "v.b")).view(T, G, dv)
     coef, every = float(m["q_temp"]["coef"]), int(m["q_temp"]["every"])
     for tt in range(T):
         pp = first_pos + tt

@@ -170,8 +170,7 @@ def test_gated_delta_rule_and_its_state(K, pdtype, H, G, d, dv, lens):
         T = rows.shape[0]
         _, _, q_start = _packed(take, at)
         o = torch.full((T, H * dv), float("nan"), dtype=torch.float32, device="cuda")
-        K.delta_rule(rows, pr, ob, oa, a_log.cuda(), dt_bias.cuda(), B, H, G, d, dv, 1e-6, q_start, _i32(slots), state, o,
-                     max_rows=max(take))
+        K.delta_rule(rows, pr, ob, oa, a_log.cuda(), dt_bias.cuda(), B, H, G, d, dv, 1e-6, q_start, _i32(slots), state, o)
         y = torch.empty((T, H * dv), dtype=tdt, device="cuda")
         K.head_norm_gate(o, H, dv, wn.cuda(), 1e-5, pr, og, "silu", y)
         n = 0

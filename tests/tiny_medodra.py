@@ -3,7 +3,7 @@
 The configurations differ in every size and option: the order of the two kinds of layer, a repeated stretch over the
 middle, over everything, over one layer, and none; head counts and groups (one key/value head, one per query head),
 values wider and narrower than keys, head sizes the tensor-core kernels take and sizes no vector load takes, short
-convolutions of one (none) to five taps, distance tables of 6 to 32 rows whose last row begins below, at and above a
+convolutions of one tap (a factor per channel) to five and none at all, distance tables of 6 to 32 rows whose last row begins below, at and above a
 cache page and at a distance that is no integer, temperatures that switch on at every position, late and never, one
 to all experts per token, layers with and without a shared expert or a feed-forward at all, residual multipliers
 and embedding scales above and below one.
@@ -28,12 +28,16 @@ def _moe(experts, top, ff, shared=None):
 def _par(heads, kv, dim, vdim, conv, scale, far, coef, every, right, mlp=None, rows=16):
     left = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": conv, "scale": scale, "bias_max": far,
             "q_temp": {"coef": coef, "every": every}}
+    if conv is None:
+        del left["conv"]
     return {"type": "parallel", "mixer": {"left": left, "right": {"width": right}}, "mlp": mlp, "_rows": rows}
 
 
 def _delta(heads, kv, dim, vdim, conv, mlp=None):
-    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": conv},
-            "mlp": mlp}
+    mixer = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": conv}
+    if conv is None:
+        del mixer["conv"]
+    return {"type": "delta", "mixer": mixer, "mlp": mlp}
 
 
 def _config(vocab, width, eps, emb_scale, mult, layers, loop=None):
@@ -57,14 +61,14 @@ MD_B = _config(300, 128, 1e-6, 0.6, 0.5, [
     _par(6, 2, 64, 64, 4, 0.125, 100, 0.3, 64, 128, _moe(8, 3, 32, 48), rows=16),
     _delta(2, 1, 64, 32, 3, _moe(2, 1, 64)),
     _par(2, 2, 64, 64, 3, 0.11, 64, 0.4, 100, 96, None, rows=12)], loop=(1, 3, 3))
-# C: head size 128 with values of 64 (widened in the cache), one key/value head, NO convolution (one tap), everything
+# C: head size 128 with values of 64 (widened in the cache), one key/value head, convolutions of one tap and none, everything
 #    twice, a table of 32 rows that reaches far beyond a page, a temperature that grows from the first position on,
 #    all experts chosen, a width that is no power of two
 MD_C = _config(257, 200, 2e-6, 14.142, 0.7, [
     _par(4, 1, 128, 64, 1, 0.09, 300, 0.1, 1, 200, _moe(2, 2, 136, 72), rows=32),
-    _delta(3, 3, 24, 40, 1, _moe(2, 2, 136, 72)),
-    _delta(2, 1, 128, 16, 2, None),
-    _par(4, 1, 128, 64, 2, 0.08, 129, 0.15, 2, 104, _moe(6, 4, 16, 8), rows=20)], loop=(0, 4, 2))
+    _delta(3, 3, 24, 40, None, _moe(2, 2, 136, 72)),
+    _delta(2, 1, 128, 16, 1, None),
+    _par(4, 1, 128, 64, None, 0.08, 129, 0.15, 2, 104, _moe(6, 4, 16, 8), rows=20)], loop=(0, 4, 2))
 # D: sizes that no vector load or tensor-core tile takes: width 72, heads of 24 with values of 10, a key/value head per
 #    query head, five taps, a table of 6 rows whose last row begins at a distance that is no integer, no temperature,
 #    one layer four times, a delta head of 40 with values of 9
@@ -162,10 +166,10 @@ def make_model(tmp_path, name: str, dtype: str = "bfloat16", strength: float = 1
                 q[h * dim + at, :] = 0.0
                 q[h * dim + at, cp] = strength / (a["scale"] * feature * feature)
                 t[p + "left.q.b"][h * dim + at] = 0.0
-                if a["conv"] > 1:
+                if a.get("conv"):
                     t[p + "left.q.conv"][h * dim + at] = 0.0
                     t[p + "left.q.conv"][h * dim + at, -1] = 1.0
-            if a["conv"] > 1:
+            if a.get("conv"):
                 t[p + "left.k.conv"][at] = 0.0
                 t[p + "left.k.conv"][at, -1] = 1.0
             t[p + "left.rel"] = torch.randn(t[p + "left.rel"].shape, generator=g)
