@@ -230,6 +230,7 @@ __global__ void __launch_bounds__(128) k_sigattn_decode(const T* KB_STEP_DATA q,
         for (int g = 0; g < SD_G; g++) a[g] = 0.0f;
         if (ok) {
             const T* kr = (const T*)cv.pool + kb_kv_offset(cv, page, 0, hk, p % KB_PAGE);
+#pragma unroll 4
             for (int e = 0; e < hd; e += NV) {
                 float kf[NV];
                 sd_load16<T>(kr + e, kf);
@@ -255,6 +256,7 @@ __global__ void __launch_bounds__(128) k_sigattn_decode(const T* KB_STEP_DATA q,
         __syncwarp();
         const int nv = min(32, k1 - r0);
         const T* vb = (const T*)cv.pool + kb_kv_offset(cv, page, 1, hk, r0 % KB_PAGE);
+#pragma unroll 4
         for (int j = 0; j < nv; j++) {
             float w[SD_G];
 #pragma unroll

@@ -361,7 +361,7 @@ def sigmoid_attention_bf16(ctx, q, out, nh, nkv, hd, scale, bias, pool, table, n
 
 def sigmoid_decode_splits(ctx, nkv: int, group: int) -> int:
     """position splits of a decode step of attention without a softmax: its CTAs are small (128 threads, a few KB of
-    shared memory), so four per SM over all (sequence, key/value head, four query heads) items; a split is at least a
-    page, and a sequence with fewer pages than splits leaves the rest empty"""
+    shared memory) and wait on loads most of the time, so eight per SM over all (sequence, key/value head, four query
+    heads) items; a split is at least a page, and a sequence with fewer pages than splits leaves the rest empty"""
     items = ctx.B * nkv * -(-group // 4)
-    return max(1, min(64, 4 * N_SM // max(1, items)))
+    return max(1, min(64, 8 * N_SM // max(1, items)))

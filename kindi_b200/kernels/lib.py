@@ -72,6 +72,9 @@ _SIGS = {
     "kb_delta_rule": [c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p,
                       c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
                       c_int, c_void_p],
+    "kb_delta_chunked": [c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p,
+                         c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                         c_void_p, c_int, c_void_p, c_int, c_void_p],
     "kb_head_norm_gate": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_longlong,
                           c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
     "kb_min_gru": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -907,12 +910,20 @@ def short_conv(a: torch.Tensor, col0: int, C: int, bias: Optional[torch.Tensor],
                                 out.stride(0), T, _stream()), "short_conv")
 
 
+DELTA_CHUNK = 64            # rows of a run (DC_C of the kernels)
+DELTA_CHUNKED = 128         # sequences that bring more rows than this run in the chunked form
+
+
 def delta_rule(qkv: torch.Tensor, proj: torch.Tensor, ob: int, oa: int, a_log: torch.Tensor, dt_bias: torch.Tensor,
                B: int, H: int, G: int, d: int, dv: int, unit_eps: float, q_start, slot, state: torch.Tensor,
-               out: torch.Tensor) -> None:
+               out: torch.Tensor, max_rows: int = 0) -> None:
     """the gated delta rule over the packed rows of ``B`` sequences. ``qkv`` float32 rows [q (G d) | k (G d) | v (H dv)];
     ``proj`` (rows or 32-bit planes) holds the beta logits at columns ``ob ..`` and the decay's at ``oa ..`` (H each);
-    ``state`` float32 [slots, >= H dv d] (rows may be strided) is read and written; ``out`` float32 [T, H dv]"""
+    ``state`` float32 [slots, >= H dv d] (rows may be strided) is read and written; ``out`` float32 [T, H dv].
+    ``max_rows`` (the most rows a sequence brings, or an upper bound) above ``DELTA_CHUNKED`` selects the form for long
+    prompts, which works a sequence in runs of ``DELTA_CHUNK`` rows (per run a triangular system that does not depend
+    on the state, solved for all runs side by side, then five small products a run); its sums differ from the
+    token-by-token form's by rounding"""
     _need_cuda(qkv, proj, a_log, dt_bias, state, out)
     n_planes, pstride, ldp = _planes_of(proj)
     assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] >= 2 * G * d + H * dv
@@ -921,6 +932,20 @@ def delta_rule(qkv: torch.Tensor, proj: torch.Tensor, ob: int, oa: int, a_log: t
     assert out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == H * dv
     if d > 256:
         raise KernelError("kindi_b200: the delta rule supports key sizes up to 256, found %d" % d)
+    if max_rows > DELTA_CHUNKED:
+        lib = load()
+        nc = -(-int(max_rows) // DELTA_CHUNK)
+        # per (sequence, run, head) the solved system, the weights of the run's own keys and three vectors; per
+        # (sequence, run, key head) the unit keys and queries, rows padded to a multiple of four
+        C, dp = DELTA_CHUNK, (d + 3) // 4 * 4
+        hs = torch.empty(B * nc * H * (2 * C * C + 3 * C), dtype=torch.float32, device=out.device)
+        qk = torch.empty(B * nc * G * 2 * C * dp, dtype=torch.float32, device=out.device)
+        _check(lib.kb_delta_chunked(_p(qkv), qkv.stride(0), _p(proj), dt(proj), n_planes, pstride, ldp, ob, oa,
+                                    _p(a_log), _p(dt_bias), B, H, G, d, dv, float(unit_eps), _p(q_start), _p(slot),
+                                    _p(state), state.stride(0), _p(hs), _p(qk), nc, _p(out), out.stride(0), _stream()),
+               "delta_chunked")
+        add_launches(1)
+        return
     _check(load().kb_delta_rule(_p(qkv), qkv.stride(0), _p(proj), dt(proj), n_planes, pstride, ldp, ob, oa, _p(a_log),
                                 _p(dt_bias), B, H, G, d, dv, float(unit_eps), _p(q_start), _p(slot), _p(state),
                                 state.stride(0), _p(out), out.stride(0), _stream()), "delta_rule")

@@ -115,8 +115,10 @@ class GatedDeltaRule(Mixer):
         c = new((ctx.T, C), dtype=torch.float32, device=y.device)
         K.short_conv(a, 0, C, None, self.w_conv, True, tails, ctx.pos, ctx.seq, ctx.slot, ctx.q_start, c)
         o = new((ctx.T, H * dv), dtype=torch.float32, device=y.device)
+        # prompts of the serving path: the chunked form (32-bit sums that differ from the token-by-token kernel's by
+        # rounding); single tokens, short steps and the true 32-bit path: token by token
         K.delta_rule(c, a, C, C + H, self.a_log, self.dt_bias, ctx.B, H, G, d, dv, self.unit_eps, ctx.q_start,
-                     ctx.slot, state, o)
+                     ctx.slot, state, o, max_rows=ctx.max_q if ctx.fast and not ctx.decode else 0)
         yn = torch.empty((ctx.T, H * dv), dtype=self.dtype, device=y.device)
         K.head_norm_gate(o, H, dv, self.g_norm, self.eps, a, C + 2 * H, "silu", yn)
         return Branch(L.planes(ctx, yn, self.w_o))

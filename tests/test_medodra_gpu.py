@@ -130,7 +130,8 @@ def _unit(x, eps):
 @pytest.mark.parametrize("pdtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,G,d,dv,lens", [(2, 1, 16, 24, [5, 1, 40]), (4, 4, 32, 64, [70, 3]), (3, 1, 40, 9, [1, 1, 1, 1]),
                                            (2, 2, 128, 16, [19, 130]), (1, 1, 256, 8, [17]),
-                                           (4, 2, 128, 128, [300, 64, 65]), (6, 2, 64, 128, [257])])
+                                           (4, 2, 128, 128, [300, 64, 65]), (6, 2, 64, 128, [257]),
+                                           (2, 1, 36, 20, [150, 20, 129])])
 def test_gated_delta_rule_and_its_state(K, pdtype, H, G, d, dv, lens):
     """S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over several sequences in one packed step, then a
     second step that goes on from the stored state (one token for some, several for others), in slots out of order
@@ -138,7 +139,8 @@ def test_gated_delta_rule_and_its_state(K, pdtype, H, G, d, dv, lens):
     g = torch.Generator().manual_seed(H * d + dv)
     tdt = DT[pdtype]
     B = len(lens)
-    more = [1 if b % 2 == 0 else 7 for b in range(B)]
+    # (the second step: one token, a few, and - from a state that is not zero - enough for the form for long prompts)
+    more = [1 if b % 2 == 0 else 200 if lens[0] == 150 else 7 for b in range(B)]
     C = 2 * G * d + H * dv
     qkv = [torch.randn(lens[b] + more[b], C, generator=g) for b in range(B)]
     proj = [(torch.randn(lens[b] + more[b], 2 + 2 * H + H * dv, generator=g) * 2).to(tdt).float() for b in range(B)]
@@ -170,7 +172,8 @@ def test_gated_delta_rule_and_its_state(K, pdtype, H, G, d, dv, lens):
         T = rows.shape[0]
         _, _, q_start = _packed(take, at)
         o = torch.full((T, H * dv), float("nan"), dtype=torch.float32, device="cuda")
-        K.delta_rule(rows, pr, ob, oa, a_log.cuda(), dt_bias.cuda(), B, H, G, d, dv, 1e-6, q_start, _i32(slots), state, o)
+        K.delta_rule(rows, pr, ob, oa, a_log.cuda(), dt_bias.cuda(), B, H, G, d, dv, 1e-6, q_start, _i32(slots), state, o,
+                     max_rows=max(take))
         y = torch.empty((T, H * dv), dtype=tdt, device="cuda")
         K.head_norm_gate(o, H, dv, wn.cuda(), 1e-5, pr, og, "silu", y)
         n = 0
