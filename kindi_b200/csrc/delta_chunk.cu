@@ -10,14 +10,13 @@
 //     S_end = G_last S0 + sum_s (G_last / G_s) k_s u_s^T.
 // k_delta_prep works every (sequence, run, head) side by side: unit vectors, beta, the decays' running products (as sums
 // of logarithms), A, its inverse by forward substitution (a thread per column) and P. k_delta_chunk then walks a
-// sequence's runs in order, a block per (sequence, head, DC_COLS columns of the state): five small products a run,
+// sequence's runs in order, a block per (sequence, head, 16 or 32 columns of the state): five small products a run,
 // every thread a few outputs, nothing passed between lanes. Rows past a sequence's end in its last run count as
 // tokens with beta = 0, g = 1 and zero vectors: they change nothing and are not written.
 #include "common.cuh"
 #include <math.h>
 
 #define DC_C 64
-#define DC_COLS 16
 #define DC_THREADS 256
 
 __device__ __forceinline__ float dc_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
@@ -182,11 +181,15 @@ __global__ void __launch_bounds__(DC_THREADS) k_delta_prep(const float* KB_STEP_
     }
 }
 
-// grid (B * H, ceil(dv / DC_COLS)). state per head [dv][d]
-__global__ void __launch_bounds__(DC_THREADS) k_delta_chunk(const float* KB_STEP_DATA qkv, int ldq, int H, int G, int d,
+// grid (B * H, ceil(dv / COLS)), DC_TB threads: thread (ty, tx) works column tx and the tokens (or state rows)
+// ty + NTY a. state per head [dv][d]. The staging loads of a run are all in flight before the first store.
+#define DC_TB 512
+template <int COLS>
+__global__ void __launch_bounds__(DC_TB) k_delta_chunk(const float* KB_STEP_DATA qkv, int ldq, int H, int G, int d,
         int dp, int dv, const int* __restrict__ q_start, const int* __restrict__ slot, float* state, size_t state_stride,
         const float* KB_STEP_DATA head_scratch, const float* KB_STEP_DATA qk_scratch, int nc, float* __restrict__ out,
         int ldo) {
+    constexpr int NTY = DC_TB / COLS, NA = DC_C / NTY;         // 32 x 2 at 16 columns, 16 x 4 at 32
     extern __shared__ __align__(16) float sm[];
     const int ld = dp + 4;
     float* ks = sm;                                    // [C][ld]
@@ -195,50 +198,83 @@ __global__ void __launch_bounds__(DC_THREADS) k_delta_chunk(const float* KB_STEP
     float* Ps = Ts + DC_C * DC_C;                      // [C][C]
     float* vec = Ps + DC_C * DC_C;                     // beta | G | G_last / G
     float* Ss = vec + 3 * DC_C;                        // [dp][COLS]
-    float* Rs = Ss + dp * DC_COLS;                     // [C][COLS]: v, then R
-    float* Us = Rs + DC_C * DC_COLS;                   // [C][COLS]
-    float* Zs = Us + DC_C * DC_COLS;                   // [C][COLS]: G_t S0^T q_t
+    float* Rs = Ss + dp * COLS;                        // [C][COLS]: v, then R
+    float* Us = Rs + DC_C * COLS;                      // [C][COLS]
+    float* Zs = Us + DC_C * COLS;                      // [C][COLS]: G_t S0^T q_t
     kb_pdl_launch();
     const int b = blockIdx.x / H, h = blockIdx.x % H, hg = h / (H / G);
-    const int e0 = blockIdx.y * DC_COLS;
-    const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+    const int e0 = blockIdx.y * COLS;
+    const int ty = threadIdx.x / COLS, tx = threadIdx.x % COLS;
     const int s0 = q_start[b], s1 = q_start[b + 1];
     float* sbase = state + (size_t)slot[b] * state_stride + (size_t)h * dv * d;
     kb_pdl_wait();
     if (s1 <= s0) return;
-    for (int idx = threadIdx.x; idx < dp * DC_COLS; idx += DC_THREADS) {
+    for (int idx = threadIdx.x; idx < dp * COLS; idx += DC_TB) {
         const int c = idx / dp, j = idx % dp;          // (a column's d elements lie together in the state)
-        Ss[j * DC_COLS + c] = (e0 + c < dv && j < d) ? sbase[(size_t)(e0 + c) * d + j] : 0.0f;
+        Ss[j * COLS + c] = (e0 + c < dv && j < d) ? sbase[(size_t)(e0 + c) * d + j] : 0.0f;
     }
     const size_t ov = (size_t)2 * G * d + (size_t)h * dv;
     const int n_runs = (s1 - s0 + DC_C - 1) / DC_C;
+    const int n_kq = DC_C * dp;                        // floats of a run's keys (and of its queries)
     for (int ci = 0; ci < n_runs; ci++) {
         const int r0 = s0 + ci * DC_C, n = min(DC_C, s1 - r0);
         const float* hs = head_scratch + (((size_t)b * nc + ci) * H + h) * DC_HEAD_FLOATS;
         const float* kq = qk_scratch + ((size_t)b * nc + ci) * G * 2 * DC_C * dp + (size_t)hg * 2 * DC_C * dp;
         __syncthreads();                               // the run before is done with the tiles
-        for (int idx = threadIdx.x * 4; idx < DC_C * dp; idx += DC_THREADS * 4) {
-            const int t = idx / dp, j = idx % dp;
-            *(float4*)&ks[t * ld + j] = *(const float4*)&kq[idx];
-            *(float4*)&qs[t * ld + j] = *(const float4*)&kq[DC_C * dp + idx];
-        }
-        for (int idx = threadIdx.x * 4; idx < 2 * DC_C * DC_C + 3 * DC_C; idx += DC_THREADS * 4)
-            *(float4*)&Ts[idx] = *(const float4*)&hs[idx];     // T^-1, P and the vectors lie in this order in both
-        for (int idx = threadIdx.x; idx < DC_C * DC_COLS; idx += DC_THREADS) {
-            const int t = idx / DC_COLS, c = idx % DC_COLS;
-            Rs[idx] = (t < n && e0 + c < dv) ? qkv[(size_t)(r0 + t) * ldq + ov + e0 + c] : 0.0f;
+        {
+            // keys and queries: up to 2 x 64 x 256 floats = 16 float4 a thread; T^-1, P and the vectors (which lie in
+            // this order in the scratch and in shared memory): 8384 floats = 5 float4 a thread
+            float4 kv4[8], qv4[8], hv4[5];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int idx = (threadIdx.x + i * DC_TB) * 4;
+                if (idx < n_kq) {
+                    kv4[i] = *(const float4*)&kq[idx];
+                    qv4[i] = *(const float4*)&kq[n_kq + idx];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 5; i++) {
+                const int idx = (threadIdx.x + i * DC_TB) * 4;
+                if (idx < DC_HEAD_FLOATS) hv4[i] = *(const float4*)&hs[idx];
+            }
+            float vv[NA];
+#pragma unroll
+            for (int a = 0; a < NA; a++) {
+                const int t = ty + NTY * a;
+                vv[a] = (t < n && e0 + tx < dv) ? qkv[(size_t)(r0 + t) * ldq + ov + e0 + tx] : 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int idx = (threadIdx.x + i * DC_TB) * 4;
+                if (idx < n_kq) {
+                    const int t = idx / dp, j = idx % dp;
+                    *(float4*)&ks[t * ld + j] = kv4[i];
+                    *(float4*)&qs[t * ld + j] = qv4[i];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 5; i++) {
+                const int idx = (threadIdx.x + i * DC_TB) * 4;
+                if (idx < DC_HEAD_FLOATS) *(float4*)&Ts[idx] = hv4[i];
+            }
+#pragma unroll
+            for (int a = 0; a < NA; a++) Rs[(ty + NTY * a) * COLS + tx] = vv[a];
         }
         __syncthreads();
-        // W = K S0, Z = Q S0: thread (ty, tx) takes tokens ty + 16 a, column tx
+        // W = K S0, Z = Q S0
         {
-            float w[4] = {0.0f, 0.0f, 0.0f, 0.0f}, z[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            for (int j = 0; j < dp; j += 4) {
-                const float c0 = Ss[j * DC_COLS + tx], c1 = Ss[(j + 1) * DC_COLS + tx];
-                const float c2 = Ss[(j + 2) * DC_COLS + tx], c3 = Ss[(j + 3) * DC_COLS + tx];
+            float w[NA], z[NA];
 #pragma unroll
-                for (int a = 0; a < 4; a++) {
-                    const float4 kv = *(const float4*)&ks[(ty + 16 * a) * ld + j];
-                    const float4 qv = *(const float4*)&qs[(ty + 16 * a) * ld + j];
+            for (int a = 0; a < NA; a++) w[a] = z[a] = 0.0f;
+#pragma unroll 2
+            for (int j = 0; j < dp; j += 4) {
+                const float c0 = Ss[j * COLS + tx], c1 = Ss[(j + 1) * COLS + tx];
+                const float c2 = Ss[(j + 2) * COLS + tx], c3 = Ss[(j + 3) * COLS + tx];
+#pragma unroll
+                for (int a = 0; a < NA; a++) {
+                    const float4 kv = *(const float4*)&ks[(ty + NTY * a) * ld + j];
+                    const float4 qv = *(const float4*)&qs[(ty + NTY * a) * ld + j];
                     w[a] = fmaf(kv.x, c0, w[a]);
                     w[a] = fmaf(kv.y, c1, w[a]);
                     w[a] = fmaf(kv.z, c2, w[a]);
@@ -250,65 +286,84 @@ __global__ void __launch_bounds__(DC_THREADS) k_delta_chunk(const float* KB_STEP
                 }
             }
 #pragma unroll
-            for (int a = 0; a < 4; a++) {
-                const int t = ty + 16 * a;
+            for (int a = 0; a < NA; a++) {
+                const int t = ty + NTY * a;
                 const float gt = vec[DC_C + t];
-                Rs[t * DC_COLS + tx] = vec[t] * (Rs[t * DC_COLS + tx] - gt * w[a]);
-                Zs[t * DC_COLS + tx] = gt * z[a];
+                Rs[t * COLS + tx] = vec[t] * (Rs[t * COLS + tx] - gt * w[a]);
+                Zs[t * COLS + tx] = gt * z[a];
             }
         }
         __syncthreads();
-        // U = T^-1 R
+        // U = T^-1 R (T^-1 is lower triangular: row t ends at column t)
         {
-            float u[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            for (int s = 0; s < DC_C; s++) {
-                const float rv = Rs[s * DC_COLS + tx];
+            float u[NA];
 #pragma unroll
-                for (int a = 0; a < 4; a++) u[a] = fmaf(Ts[(ty + 16 * a) * DC_C + s], rv, u[a]);
+            for (int a = 0; a < NA; a++) u[a] = 0.0f;
+            const int s_end = min(DC_C, ty + NTY * (NA - 1) + 1);
+#pragma unroll 4
+            for (int s = 0; s < s_end; s++) {
+                const float rv = Rs[s * COLS + tx];
+#pragma unroll
+                for (int a = 0; a < NA; a++) u[a] = fmaf(Ts[(ty + NTY * a) * DC_C + s], rv, u[a]);
             }
 #pragma unroll
-            for (int a = 0; a < 4; a++) Us[(ty + 16 * a) * DC_COLS + tx] = u[a];
+            for (int a = 0; a < NA; a++) Us[(ty + NTY * a) * COLS + tx] = u[a];
         }
         __syncthreads();
         // o = Z + P U; S <- G_last S + sum_s (G_last / G_s) k_s u_s^T
         {
-            float o[4];
+            float o[NA];
 #pragma unroll
-            for (int a = 0; a < 4; a++) o[a] = Zs[(ty + 16 * a) * DC_COLS + tx];
-            for (int s = 0; s < DC_C; s++) {
-                const float uv = Us[s * DC_COLS + tx];
+            for (int a = 0; a < NA; a++) o[a] = Zs[(ty + NTY * a) * COLS + tx];
+            const int s_end = min(DC_C, ty + NTY * (NA - 1) + 1);
+#pragma unroll 4
+            for (int s = 0; s < s_end; s++) {
+                const float uv = Us[s * COLS + tx];
 #pragma unroll
-                for (int a = 0; a < 4; a++) o[a] = fmaf(Ps[(ty + 16 * a) * DC_C + s], uv, o[a]);
+                for (int a = 0; a < NA; a++) o[a] = fmaf(Ps[(ty + NTY * a) * DC_C + s], uv, o[a]);
             }
 #pragma unroll
-            for (int a = 0; a < 4; a++) {
-                const int t = ty + 16 * a;
+            for (int a = 0; a < NA; a++) {
+                const int t = ty + NTY * a;
                 if (t < n && e0 + tx < dv) out[(size_t)(r0 + t) * ldo + (size_t)h * dv + e0 + tx] = o[a];
             }
             const float gl = vec[DC_C + DC_C - 1];
-            for (int j0 = 0; j0 < dp; j0 += 64) {
-                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                for (int s = 0; s < DC_C; s++) {
-                    const float uv = Us[s * DC_COLS + tx] * vec[2 * DC_C + s];
+            for (int j0 = 0; j0 < dp; j0 += DC_C) {
+                float acc[NA];
 #pragma unroll
-                    for (int a = 0; a < 4; a++) {
-                        const int j = j0 + ty + 16 * a;
+                for (int a = 0; a < NA; a++) acc[a] = 0.0f;
+#pragma unroll 4
+                for (int s = 0; s < DC_C; s++) {
+                    const float uv = Us[s * COLS + tx] * vec[2 * DC_C + s];
+#pragma unroll
+                    for (int a = 0; a < NA; a++) {
+                        const int j = j0 + ty + NTY * a;
                         if (j < dp) acc[a] = fmaf(ks[s * ld + j], uv, acc[a]);
                     }
                 }
 #pragma unroll
-                for (int a = 0; a < 4; a++) {
-                    const int j = j0 + ty + 16 * a;
-                    if (j < dp) Ss[j * DC_COLS + tx] = fmaf(gl, Ss[j * DC_COLS + tx], acc[a]);
+                for (int a = 0; a < NA; a++) {
+                    const int j = j0 + ty + NTY * a;
+                    if (j < dp) Ss[j * COLS + tx] = fmaf(gl, Ss[j * COLS + tx], acc[a]);
                 }
             }
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < dp * DC_COLS; idx += DC_THREADS) {
+    for (int idx = threadIdx.x; idx < dp * COLS; idx += DC_TB) {
         const int c = idx / dp, j = idx % dp;
-        if (e0 + c < dv && j < d) sbase[(size_t)(e0 + c) * d + j] = Ss[j * DC_COLS + c];
+        if (e0 + c < dv && j < d) sbase[(size_t)(e0 + c) * d + j] = Ss[j * COLS + c];
     }
+}
+
+static int dc_sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
 }
 
 // head_scratch: B * nc * H * DC_HEAD_FLOATS floats; qk_scratch: B * nc * G * 2 * DC_C * dp floats, dp = d rounded up to a
@@ -322,16 +377,20 @@ extern "C" int kb_delta_chunked(const float* qkv, int ldq, const void* proj, int
     if (d > 256 || G <= 0 || H % G || nc > 65535 || B > 65535 || H > 65535) return (int)cudaErrorInvalidValue;
     const int dp = (d + 3) / 4 * 4, ld = dp + 4;
     const size_t sm_a = (size_t)(2 * DC_C * ld + 2 * DC_C * (DC_C + 1) + 2 * DC_C) * sizeof(float);
-    const size_t sm_b = (size_t)(2 * DC_C * ld + 2 * DC_C * DC_C + 3 * DC_C + dp * DC_COLS + 3 * DC_C * DC_COLS) * sizeof(float);
-    static char tag_a32, tag_a16, tag_b;
+    // 16 columns of the state a block; 32 when that would be more blocks than SMs (a block fills an SM)
+    const int cols = (long long)B * H * ((dv + 15) / 16) > dc_sm_count() ? 32 : 16;
+    const size_t sm_b = (size_t)(2 * DC_C * ld + 2 * DC_C * DC_C + 3 * DC_C + dp * cols + 3 * DC_C * cols) * sizeof(float);
+    static char tag_a32, tag_a16, tag_b16, tag_b32;
     if (kb_first_use(pdtype == KB_F32 ? &tag_a32 : &tag_a16)) {
         cudaError_t e = pdtype == KB_F32
             ? cudaFuncSetAttribute(k_delta_prep<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
             : cudaFuncSetAttribute(k_delta_prep<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return (int)e;
     }
-    if (kb_first_use(&tag_b)) {
-        cudaError_t e = cudaFuncSetAttribute(k_delta_chunk, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (kb_first_use(cols == 16 ? &tag_b16 : &tag_b32)) {
+        cudaError_t e = cols == 16
+            ? cudaFuncSetAttribute(k_delta_chunk<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
+            : cudaFuncSetAttribute(k_delta_chunk<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid_a(nc, H, B);
@@ -343,8 +402,12 @@ extern "C" int kb_delta_chunked(const float* qkv, int ldq, const void* proj, int
         kb_launch(k_delta_prep<bf16>, grid_a, DC_THREADS, sm_a, st, qkv, ldq, (const bf16*)proj, n_planes,
                   (size_t)plane_stride, ldp, ob, oa, a_log, dt_bias, H, G, d, dp, unit_eps, q_start, head_scratch,
                   qk_scratch, nc);
-    dim3 grid_b(B * H, (dv + DC_COLS - 1) / DC_COLS);
-    kb_launch(k_delta_chunk, grid_b, DC_THREADS, sm_b, st, qkv, ldq, H, G, d, dp, dv, q_start, slot, state,
-              (size_t)state_stride, (const float*)head_scratch, (const float*)qk_scratch, nc, out, ldo);
+    dim3 grid_b(B * H, (dv + cols - 1) / cols);
+    if (cols == 16)
+        kb_launch(k_delta_chunk<16>, grid_b, DC_TB, sm_b, st, qkv, ldq, H, G, d, dp, dv, q_start, slot, state,
+                  (size_t)state_stride, (const float*)head_scratch, (const float*)qk_scratch, nc, out, ldo);
+    else
+        kb_launch(k_delta_chunk<32>, grid_b, DC_TB, sm_b, st, qkv, ldq, H, G, d, dp, dv, q_start, slot, state,
+                  (size_t)state_stride, (const float*)head_scratch, (const float*)qk_scratch, nc, out, ldo);
     KB_LAUNCH_RET();
 }
