@@ -17,9 +17,12 @@ weighted sums of values go through ``W_o`` (+ bias), which the branch carries as
 The three projections are one product. The convolution, the temperature, the value norm, scores, weights and sums are
 32-bit. The bias table and the per-head constant are folded into one table over the distance when the part is built
 (64-bit on the host): ``[H, ceil(far) + 1]``, whose last entry stands for every larger distance. The cache and the
-kernels know one head size: keys and values are stored ``max(head_dim, v_head_dim)`` wide, rounded up to 64 or 128 (the
-head sizes of the tensor-core kernel for prompts) or, beyond 128, to a multiple of eight, zero beyond their own size. Sizes, ``scale``, ``conv``, ``bias``, ``q_temp``, ``v_norm``, ``rel`` (``{"name",
-"far"}`` and optionally ``"rows"``; without it the table's own shape gives its rows), ``head_bias`` and the tensors' suffixes (``names``) are parameters of the part.
+kernels know one head size: keys and values are stored ``max(head_dim, v_head_dim)`` wide, rounded up to 64 or 128
+(the head sizes of the tensor-core kernel for prompts) or, beyond 128, to a multiple of eight, zero beyond their own
+size. ``conv``: the taps of the tensors ``<projection>.conv`` (one tap is a factor per channel; absent or 0: no
+convolution). Sizes, ``scale``, ``conv``, ``bias``, ``q_temp``, ``v_norm``, ``rel`` (``{"name", "far"}`` and
+optionally ``"rows"``; without it the table's own shape gives its rows), ``head_bias`` and the tensors' suffixes
+(``names``) are parameters of the part.
 """
 from __future__ import annotations
 
