@@ -294,58 +294,76 @@ __global__ void __launch_bounds__(DC_TB) k_delta_chunk(const float* KB_STEP_DATA
             }
         }
         __syncthreads();
-        // U = T^-1 R (T^-1 is lower triangular: row t ends at column t)
+        // U = T^-1 R (T^-1 and P are lower triangular: row t ends at column t), four columns of a row a load
+        const int s_end = min(DC_C, (ty + NTY * (NA - 1) + 4) & ~3);
         {
             float u[NA];
 #pragma unroll
             for (int a = 0; a < NA; a++) u[a] = 0.0f;
-            const int s_end = min(DC_C, ty + NTY * (NA - 1) + 1);
-#pragma unroll 4
-            for (int s = 0; s < s_end; s++) {
-                const float rv = Rs[s * COLS + tx];
+#pragma unroll 2
+            for (int s = 0; s < s_end; s += 4) {
+                const float r0v = Rs[s * COLS + tx], r1v = Rs[(s + 1) * COLS + tx];
+                const float r2v = Rs[(s + 2) * COLS + tx], r3v = Rs[(s + 3) * COLS + tx];
 #pragma unroll
-                for (int a = 0; a < NA; a++) u[a] = fmaf(Ts[(ty + NTY * a) * DC_C + s], rv, u[a]);
+                for (int a = 0; a < NA; a++) {
+                    const float4 tv = *(const float4*)&Ts[(ty + NTY * a) * DC_C + s];
+                    u[a] = fmaf(tv.x, r0v, u[a]);
+                    u[a] = fmaf(tv.y, r1v, u[a]);
+                    u[a] = fmaf(tv.z, r2v, u[a]);
+                    u[a] = fmaf(tv.w, r3v, u[a]);
+                }
             }
 #pragma unroll
             for (int a = 0; a < NA; a++) Us[(ty + NTY * a) * COLS + tx] = u[a];
         }
         __syncthreads();
-        // o = Z + P U; S <- G_last S + sum_s (G_last / G_s) k_s u_s^T
+        // o = Z + P U; R is done with: its place takes u_s (G_last / G_s) for the state's update
         {
             float o[NA];
 #pragma unroll
-            for (int a = 0; a < NA; a++) o[a] = Zs[(ty + NTY * a) * COLS + tx];
-            const int s_end = min(DC_C, ty + NTY * (NA - 1) + 1);
-#pragma unroll 4
-            for (int s = 0; s < s_end; s++) {
-                const float uv = Us[s * COLS + tx];
+            for (int a = 0; a < NA; a++) {
+                const int t = ty + NTY * a;
+                o[a] = Zs[t * COLS + tx];
+                Rs[t * COLS + tx] = Us[t * COLS + tx] * vec[2 * DC_C + t];
+            }
+#pragma unroll 2
+            for (int s = 0; s < s_end; s += 4) {
+                const float u0 = Us[s * COLS + tx], u1 = Us[(s + 1) * COLS + tx];
+                const float u2 = Us[(s + 2) * COLS + tx], u3 = Us[(s + 3) * COLS + tx];
 #pragma unroll
-                for (int a = 0; a < NA; a++) o[a] = fmaf(Ps[(ty + NTY * a) * DC_C + s], uv, o[a]);
+                for (int a = 0; a < NA; a++) {
+                    const float4 pv = *(const float4*)&Ps[(ty + NTY * a) * DC_C + s];
+                    o[a] = fmaf(pv.x, u0, o[a]);
+                    o[a] = fmaf(pv.y, u1, o[a]);
+                    o[a] = fmaf(pv.z, u2, o[a]);
+                    o[a] = fmaf(pv.w, u3, o[a]);
+                }
             }
 #pragma unroll
             for (int a = 0; a < NA; a++) {
                 const int t = ty + NTY * a;
                 if (t < n && e0 + tx < dv) out[(size_t)(r0 + t) * ldo + (size_t)h * dv + e0 + tx] = o[a];
             }
+        }
+        __syncthreads();
+        // S <- G_last S + sum_s k_s (u_s G_last / G_s)^T: thread (ty, tx) takes four neighbouring rows of column tx
+        {
             const float gl = vec[DC_C + DC_C - 1];
-            for (int j0 = 0; j0 < dp; j0 += DC_C) {
-                float acc[NA];
-#pragma unroll
-                for (int a = 0; a < NA; a++) acc[a] = 0.0f;
+            for (int j = 4 * ty; j < dp; j += 4 * NTY) {
+                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll 4
                 for (int s = 0; s < DC_C; s++) {
-                    const float uv = Us[s * COLS + tx] * vec[2 * DC_C + s];
-#pragma unroll
-                    for (int a = 0; a < NA; a++) {
-                        const int j = j0 + ty + NTY * a;
-                        if (j < dp) acc[a] = fmaf(ks[s * ld + j], uv, acc[a]);
-                    }
+                    const float uv = Rs[s * COLS + tx];
+                    const float4 kv = *(const float4*)&ks[s * ld + j];
+                    a0 = fmaf(kv.x, uv, a0);
+                    a1 = fmaf(kv.y, uv, a1);
+                    a2 = fmaf(kv.z, uv, a2);
+                    a3 = fmaf(kv.w, uv, a3);
                 }
-#pragma unroll
-                for (int a = 0; a < NA; a++) {
-                    const int j = j0 + ty + NTY * a;
-                    if (j < dp) Ss[j * COLS + tx] = fmaf(gl, Ss[j * COLS + tx], acc[a]);
-                }
+                Ss[j * COLS + tx] = fmaf(gl, Ss[j * COLS + tx], a0);
+                Ss[(j + 1) * COLS + tx] = fmaf(gl, Ss[(j + 1) * COLS + tx], a1);
+                Ss[(j + 2) * COLS + tx] = fmaf(gl, Ss[(j + 2) * COLS + tx], a2);
+                Ss[(j + 3) * COLS + tx] = fmaf(gl, Ss[(j + 3) * COLS + tx], a3);
             }
         }
     }
