@@ -401,7 +401,7 @@ def _edge_requests(raw, seed, longest=420):
     rng = random.Random(seed)
     vocab = raw["vocab"]
     edges = [e for e in _table_edges(raw) if e < longest - 60]
-    L = min(longest, max(edges) + 150)
+    L = min(longest, max(edges, default=70) + 150)        # (a model of delta layers alone has no table)
     places = {0, 1, 63, 64, 127, 128}
     for e in edges:
         places |= {L - 3 - e, L - 2 - e, L - 1 - e, L - e}
