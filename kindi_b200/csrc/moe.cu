@@ -149,12 +149,171 @@ extern "C" int kb_moe_topk(const float* logits, int ldz, const float* bias, int 
     KB_LAUNCH_RET();
 }
 
+// The pick of a router whose scores are the softmax over ALL its outputs: s = softmax(z) over n outputs, choice scores
+// c = s + correction; the outputs form `groups` equal groups of neighbours, a group's score is its largest c, and only
+// outputs of the `keep` best groups can be chosen (groups == 1: all); the `top` largest c among those are taken one
+// after the other (of equal values the lower index first); the weights are the chosen outputs' s over their sum
+// (+ 1e-20). One warp per row, lane l holding outputs l, l + 32, ... (up to 32 * MOE_PER outputs, up to 32 groups).
+// Outputs from n_experts on are "identity experts" of the caller: the pick treats them like any other.
+__global__ void __launch_bounds__(128) k_moe_route_warp(const float* KB_STEP_DATA logits, int ldz,
+        const float* __restrict__ correction, int T, int n, int top, int groups, int keep, int* __restrict__ idx,
+        float* __restrict__ wts) {
+    kb_pdl_launch();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    float b[MOE_PER];
+#pragma unroll
+    for (int j = 0; j < MOE_PER; j++) b[j] = (correction && lane + 32 * j < n) ? correction[lane + 32 * j] : 0.0f;
+    kb_pdl_wait();
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * ldz;
+    float s[MOE_PER], v[MOE_PER];
+    bool free_[MOE_PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < MOE_PER; j++) {
+        const int e = lane + 32 * j;
+        free_[j] = e < n;
+        s[j] = free_[j] ? z[e] : -INFINITY;
+        mx = fmaxf(mx, s[j]);
+    }
+    mx = kb_warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < MOE_PER; j++) {
+        s[j] = free_[j] ? expf(s[j] - mx) : 0.0f;
+        sum += s[j];
+    }
+    sum = kb_warp_sum(sum);
+#pragma unroll
+    for (int j = 0; j < MOE_PER; j++) {
+        s[j] = s[j] / sum;
+        v[j] = s[j] + b[j];
+    }
+    if (groups > 1) {
+        // lane g keeps group g's score; then `keep` rounds take the best group not yet taken
+        const int size = n / groups;
+        float gs = 0.0f;
+        for (int g = 0; g < groups; g++) {
+            float m = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < MOE_PER; j++)
+                if (free_[j] && (lane + 32 * j) / size == g) m = fmaxf(m, v[j]);
+            m = kb_warp_max(m);
+            if (lane == g) gs = m;
+        }
+        bool gfree = lane < groups;
+        unsigned kept = 0u;
+        for (int k = 0; k < keep; k++) {
+            float bv = gs;
+            int bg = gfree ? lane : 32;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+                if (og < 32 && (bg == 32 || ov > bv || (ov == bv && og < bg) || (bv != bv && og < bg))) {
+                    bv = ov;
+                    bg = og;
+                }
+            }
+            if (bg < 32) kept |= 1u << bg;
+            if (lane == bg) gfree = false;
+        }
+#pragma unroll
+        for (int j = 0; j < MOE_PER; j++)
+            if (free_[j] && !((kept >> ((lane + 32 * j) / size)) & 1u)) free_[j] = false;
+    }
+    float my_s = 0.0f;
+    int my_idx = 0;
+    for (int k = 0; k < top; k++) {
+        int be = n;
+        float bv = 0.0f, bs = 0.0f;
+#pragma unroll
+        for (int j = 0; j < MOE_PER; j++) {
+            const int e = lane + 32 * j;
+            if (free_[j] && (be == n || v[j] > bv)) {
+                be = e;
+                bv = v[j];
+                bs = s[j];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (oe < n && (be == n || ov > bv || (ov == bv && oe < be) || (bv != bv && oe < be))) {
+                bv = ov;
+                bs = os;
+                be = oe;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < MOE_PER; j++)
+            if (lane + 32 * j == be) free_[j] = false;
+        if (lane == k) {
+            my_s = bs;
+            my_idx = be;
+        }
+    }
+    float tot = 0.0f;                               // summed in the order they were chosen
+    for (int k = 0; k < top; k++) tot += __shfl_sync(0xffffffffu, my_s, k);
+    if (lane < top) {
+        // (fewer free outputs than `top`: the kept groups are too small; the pick names no expert and weighs nothing)
+        idx[(size_t)t * top + lane] = my_idx < n ? my_idx : -1;
+        wts[(size_t)t * top + lane] = my_idx < n ? my_s / (tot + 1e-20f) : 0.0f;
+    }
+}
+
+extern "C" int kb_moe_route(const float* logits, int ldz, const float* correction, int T, int n, int top, int groups,
+                            int keep, int* idx, float* wts, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (top < 1 || top > 32 || top > n || n > 32 * MOE_PER || groups < 1 || groups > 32 || n % groups || keep < 1 ||
+        keep > groups)
+        return (int)cudaErrorInvalidValue;
+    kb_launch(k_moe_route_warp, (T + 3) / 4, 128, 0, st, logits, ldz, correction, T, n, top, groups, keep, idx, wts);
+    KB_LAUNCH_RET();
+}
+
+// Picks that name an "identity expert" (an index from n_experts on) have no product: plane k of the pair's token is
+// the pick's weight times the expert's input row itself. Picks below n_experts are left to the grouped products;
+// a pick that names nothing (-1) gets zeros.
+template <typename TY>
+__global__ void __launch_bounds__(256) k_moe_identity(const TY* KB_STEP_DATA y, int ldy, const int* KB_STEP_DATA idx,
+        const float* KB_STEP_DATA wts, float* planes, size_t plane_stride, int n_pairs, int top, int n_experts,
+        int width) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int pair = blockIdx.x;
+    const int e = idx[pair];
+    if (e >= 0 && e < n_experts) return;
+    const float w = e < 0 ? 0.0f : wts[pair];
+    const size_t t = pair / top;
+    float* dst = planes + (size_t)(pair % top) * plane_stride + t * width;
+    for (int c = threadIdx.x; c < width; c += 256) dst[c] = e < 0 ? 0.0f : __fmul_rn(w, kb_to_f<TY>(y[t * ldy + c]));
+}
+
+extern "C" int kb_moe_identity(const void* y, int ydtype, int ldy, const int* idx, const float* wts, float* planes,
+                               long long plane_stride, int n_pairs, int top, int n_experts, int width,
+                               cudaStream_t st) {
+    if (n_pairs <= 0) return 0;
+    if (ydtype == KB_F32)
+        kb_launch(k_moe_identity<float>, n_pairs, 256, 0, st, (const float*)y, ldy, idx, wts, planes,
+                  (size_t)plane_stride, n_pairs, top, n_experts, width);
+    else if (ydtype == KB_BF16)
+        kb_launch(k_moe_identity<bf16>, n_pairs, 256, 0, st, (const bf16*)y, ldy, idx, wts, planes,
+                  (size_t)plane_stride, n_pairs, top, n_experts, width);
+    else return (int)cudaErrorInvalidValue;
+    KB_LAUNCH_RET();
+}
+
 #define MOE_PLAN_THREADS 1024
 // shared: counts[E], cursor[E]
 __global__ void __launch_bounds__(MOE_PLAN_THREADS) k_moe_plan(const int* KB_STEP_DATA idx, int n_pairs, int E,
         int tile, int* __restrict__ offs, int* __restrict__ perm, int* __restrict__ tile_e,
         int* __restrict__ tile_r0, int* __restrict__ n_tiles) {
     extern __shared__ int sh[];
+    __shared__ int s_total;
     int* counts = sh;
     int* cursor = sh + E;
     kb_pdl_launch();
@@ -180,12 +339,16 @@ __global__ void __launch_bounds__(MOE_PLAN_THREADS) k_moe_plan(const int* KB_STE
         }
         offs[E] = at;
         n_tiles[0] = nt;
+        s_total = at;
     }
     __syncthreads();
     for (int p = threadIdx.x; p < n_pairs; p += MOE_PLAN_THREADS) {
         const int e = idx[p];
         if (e >= 0 && e < E) perm[atomicAdd(&cursor[e], 1)] = p;
     }
+    // pairs that name no expert of these products (an index outside 0..E-1) have no place in the order: the rest of
+    // the list names pair 0, so that a kernel that walks all n_pairs entries reads a row that exists
+    for (int p = s_total + threadIdx.x; p < n_pairs; p += MOE_PLAN_THREADS) perm[p] = 0;
 }
 
 extern "C" int kb_moe_plan(const int* idx, int n_pairs, int E, int tile, int* offs, int* perm, int* tile_e,

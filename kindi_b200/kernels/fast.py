@@ -304,14 +304,15 @@ def _moe_tc_ok(y, wup, wdown) -> bool:
             and y.stride(1) == 1 and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0)
 
 
-def _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T, gated=False, weight_on="output"):
+def _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T, gated=False, weight_on="output", act_params=None):
     E, F, width = wup.shape
     h = torch.empty((T * top, F), dtype=torch.bfloat16, device=ys.device)
     if gated:
         # [gate | up] of every pair, then act(w g) * (w u) with the pick's weight on the expert's input (or 1)
         K.moe_gemm_tc(ys, wup, h, plan, None, top, "none", up=True, bn=_moe_bn(F, T * top), status=ctx.status)
         gu, h = h, torch.empty((T * top, F // 2), dtype=torch.bfloat16, device=ys.device)
-        K.moe_gate_mul(gu, wts if weight_on == "input" else None, plan, act, h)
+        from . import moe as M
+        M.gate_mul(gu, wts if weight_on == "input" else None, plan, act, h, act_params)
     else:
         K.moe_gemm_tc(ys, wup, h, plan, None, top, act, up=True, bn=_moe_bn(F, T * top), status=ctx.status)
     planes = torch.empty((top, T, width), dtype=torch.float32, device=ys.device)
@@ -334,7 +335,7 @@ def _ones_like(wts: torch.Tensor) -> torch.Tensor:
     return t
 
 
-def moe_experts(ctx, y, idx, wts, wup, wdown, top, act, gated=False, weight_on="output"):
+def moe_experts(ctx, y, idx, wts, wup, wdown, top, act, gated=False, weight_on="output", act_params=None):
     """the experts' grouped products on the tensor cores, where the kernel takes the shape (bf16, width and expert
     size multiples of 8): 32-bit planes [top, T, width]; None: not taken"""
     T, width = y.shape
@@ -344,7 +345,7 @@ def moe_experts(ctx, y, idx, wts, wup, wdown, top, act, gated=False, weight_on="
     plan = K.moe_plan(idx, E, K.moe_gemm_tc_tile())
     ys = torch.empty((T * top, width), dtype=torch.bfloat16, device=y.device)
     K.moe_gather(y, ys, plan, top)
-    return _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T, gated, weight_on)
+    return _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T, gated, weight_on, act_params)
 
 
 def sigmoid_attention_bf16(ctx, q, out, nh, nkv, hd, scale, bias, pool, table, n_pages) -> bool:

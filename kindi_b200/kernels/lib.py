@@ -122,6 +122,22 @@ _SIGS = {
                   c_void_p],
     "kb_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_float, c_void_p],
     "kb_wait_selftest": [ctypes.c_ulonglong, c_void_p, c_void_p, c_void_p],
+    "kb_headnorm_rope_store": [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                               c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                               c_void_p],
+    "kb_diff_combine": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                        c_float, c_void_p],
+    "kb_head_gate_mul": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int,
+                         c_int, c_int, c_void_p],
+    "kb_postnorm_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p,
+                        c_int, c_int, c_int, c_void_p],
+    "kb_cast_rows": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    "kb_glu_clamp": [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                     c_float, c_void_p],
+    "kb_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "kb_moe_identity": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                        c_void_p],
 }
 
 
@@ -1098,3 +1114,125 @@ def sigattn_tc(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int
     _check(load().kb_sigattn_tc(_p(q), q.stride(0), _p(out), out.stride(0), _p(slot), _p(q_start), _p(kv_len), B, nh,
                                 nkv, hd, float(scale), _p(bias), bias.shape[1] if bias is not None else 0, _p(pool),
                                 _p(table), table.stride(0), n_pages, grid_x, _p(status), _stream()), "sigattn_tc")
+
+
+# ------------------------------------------------------------------------------- per-head steps, norm on the output
+def headnorm_rope_store(qkv: torch.Tensor, qout: torch.Tensor, gq: Optional[torch.Tensor], gk: Optional[torch.Tensor],
+                        eps: float, dim_true: int, norm: str, inv_freq: Optional[torch.Tensor],
+                        inv_freq64: Optional[torch.Tensor], rot: int, t_coef: float, t_every: int, pos, seq, slot,
+                        nh: int, nkv: int, nkv_store: int, hd: int, pool: Optional[torch.Tensor], table: torch.Tensor,
+                        n_pages: int, status: torch.Tensor) -> None:
+    """every query and key head of a row through its OWN root-mean-square norm over ``dim_true`` elements (``norm``:
+    "none", "before" or "after" the rotation; gains ``gq`` / ``gk`` float32 [hd] shared by the heads, None for a unit
+    norm), the rotation of the pairs (i, i + rot/2), and on queries the temperature ``1 + t_coef ln(floor((pos + 1) /
+    t_every) + 1)``; queries to ``qout``, keys and values into their pages. qkv: rows or 32-bit planes of [q heads |
+    k heads | v heads]. float32 rows rotate by ``inv_freq64`` (float64), everything else by ``inv_freq``"""
+    _need_cuda(qkv, qout, gq, gk, inv_freq, inv_freq64, pool, table)
+    planes = qkv.shape[0] if qkv.dim() == 3 else 1
+    T = qkv.shape[-2]
+    assert qkv.stride(-1) == 1 and qkv.shape[-1] >= (nh + 2 * nkv) * hd and qout.stride(1) == 1
+    for g in (gq, gk):
+        assert g is None or (g.dtype == torch.float32 and g.numel() == hd and g.is_contiguous())
+    assert (gq is None) == (gk is None)
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot // 2)
+    assert inv_freq64 is None or (inv_freq64.dtype == torch.float64 and inv_freq64.numel() >= rot // 2)
+    if nkv_store:
+        assert pool is not None and pool.dtype == qout.dtype and pool.is_contiguous() and nkv_store == nkv
+    pstride = qkv.stride(0) if qkv.dim() == 3 else 0
+    mode = {"none": 0, "before": 1, "after": 2}[norm]
+    rc = load().kb_headnorm_rope_store(_p(qkv), dt(qkv), planes, pstride, qkv.stride(-2), _p(qout), dt(qout),
+                                       qout.stride(0), _p(gq), _p(gk), float(eps), int(dim_true), mode, _p(inv_freq),
+                                       _p(inv_freq64), int(rot), float(t_coef), int(t_every), _p(pos), _p(seq),
+                                       _p(slot), T, nh, nkv, nkv_store, hd, _p(pool), _p(table), table.stride(0),
+                                       n_pages, _p(status), _stream())
+    _check(rc, "headnorm_rope_store")
+
+
+def diff_combine(a: torch.Tensor, out: torch.Tensor, H: int, r: int, hd: int, vd: int, lam: float, eps: float,
+                 mult: float) -> None:
+    """out[t][h] = unit-RMS(a[t][g][0][i] - lam a[t][g][1][i]) * mult over the head's first ``vd`` values (zero
+    beyond), h = g r + i; ``a`` holds 2 H heads of ``hd`` in the order (group, map, head of the group)"""
+    _need_cuda(a, out)
+    T = a.shape[0]
+    assert a.shape[1] == 2 * H * hd and out.shape == (T, H * hd) and a.stride(1) == 1 and out.stride(1) == 1
+    assert a.dtype == out.dtype
+    _check(load().kb_diff_combine(_p(a), dt(a), a.stride(0), _p(out), out.stride(0), T, H, r, hd, vd, float(lam),
+                                  float(eps), float(mult), _stream()), "diff_combine")
+
+
+def head_gate_mul(a: torch.Tensor, g: torch.Tensor, out: torch.Tensor, hd: int) -> None:
+    """out[t][h hd + c] = a[t][h hd + c] * sigmoid(g[t][h]); ``g``: rows [T, >= H] or 32-bit planes [S, T, >= H]"""
+    _need_cuda(a, g, out)
+    T, N = a.shape
+    n_planes, pstride, ldg = _planes_of(g)
+    assert N % hd == 0 and g.shape[-1] >= N // hd and g.shape[-2] == T and out.shape == (T, N)
+    assert a.stride(1) == 1 and out.stride(1) == 1 and out.dtype == a.dtype
+    _check(load().kb_head_gate_mul(_p(a), dt(a), a.stride(0), _p(g), dt(g), n_planes, pstride, ldg, _p(out),
+                                   out.stride(0), T, N, hd, _stream()), "head_gate_mul")
+
+
+def postnorm_add(x: torch.Tensor, delta: torch.Tensor, bias: Optional[torch.Tensor], w: torch.Tensor,
+                 ls: Optional[torch.Tensor], eps: float, y: Optional[torch.Tensor]) -> None:
+    """x += ls * (w * rms(sum of the planes ``delta`` [S, T, E] + bias)), in place; ``y`` (when given, [T, E] in a run
+    dtype) receives the new x"""
+    _need_cuda(x, delta, bias, w, ls, y)
+    T, E = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous() and delta.dtype == torch.float32 and delta.dim() == 3
+    assert delta.shape[1:] == (T, E) and delta.stride(2) == 1 and delta.stride(1) == E
+    assert w.numel() == E and w.is_contiguous() and (ls is None or (ls.numel() == E and ls.is_contiguous()
+                                                                    and ls.dtype == w.dtype))
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous())
+    assert y is None or (y.shape == (T, E) and y.is_contiguous())
+    _check(load().kb_postnorm_add(_p(x), _p(delta), delta.shape[0], delta.stride(0), _p(bias), _p(w), _p(ls), dt(w),
+                                  float(eps), _p(y), dt(y) if y is not None else F32, T, E, _stream()), "postnorm_add")
+
+
+def cast_rows(x: torch.Tensor, y: torch.Tensor) -> None:
+    """y = x (float32, contiguous) in y's dtype"""
+    _need_cuda(x, y)
+    assert x.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
+    _check(load().kb_cast_rows(_p(x), _p(y), dt(y), x.numel(), _stream()), "cast_rows")
+
+
+def glu_clamp(gu: torch.Tensor, out: torch.Tensor, group: int, limit: float, alpha: float) -> None:
+    """out = g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit); ``gu``: rows
+    [R, 2F] or 32-bit planes [S, R, 2F], gate and up columns in groups of ``group`` (group = F: all gates, then all
+    ups)"""
+    _need_cuda(gu, out)
+    R, F = out.shape
+    n_planes, pstride, ldg = _planes_of(gu)
+    assert gu.shape[-2] == R and gu.shape[-1] == 2 * F and out.stride(1) == 1 and F % group == 0
+    _check(load().kb_glu_clamp(_p(gu), dt(gu), n_planes, pstride, ldg, _p(out), dt(out), out.stride(0), R, F, group,
+                               float(limit), float(alpha), _stream()), "glu_clamp")
+
+
+def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], n: int, top: int, groups: int, keep: int):
+    """the pick of a router that scores by the softmax over all its ``n`` outputs (the first n columns of float32
+    ``logits``): choice by score + ``correction`` inside the ``keep`` best of ``groups`` groups of neighbours, weights
+    the chosen scores over their sum: (idx int32 [T, top], weights float32 [T, top])"""
+    _need_cuda(logits, correction)
+    T = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= n
+    if correction is not None:
+        assert correction.dtype == torch.float32 and correction.numel() == n and correction.is_contiguous()
+    if n > 256 or groups > 32 or n % groups or not (1 <= keep <= groups) or not (1 <= top <= min(32, n)):
+        raise KernelError("kindi_b200: the grouped router pick takes up to 256 outputs in up to 32 equal groups and "
+                          "up to 32 picks a row; found %d outputs, %d groups (keep %d), top %d" % (n, groups, keep, top))
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _check(load().kb_moe_route(_p(logits), logits.stride(0), _p(correction), T, n, top, groups, keep, _p(idx),
+                               _p(wts), _stream()), "moe_route")
+    return idx, wts
+
+
+def moe_identity(y: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, planes: torch.Tensor, n_experts: int) -> None:
+    """planes[k][t] = wts[t][k] * y[t] for every pick that names an index from ``n_experts`` on (an expert that hands
+    its input through); picks below are left as they are"""
+    _need_cuda(y, idx, wts, planes)
+    T, width = y.shape
+    top = idx.shape[1]
+    assert y.stride(1) == 1 and idx.is_contiguous() and wts.is_contiguous() and idx.shape == wts.shape == (T, top)
+    assert planes.dtype == torch.float32 and planes.shape == (top, T, width) and planes.stride(2) == 1
+    assert planes.stride(1) == width
+    _check(load().kb_moe_identity(_p(y), dt(y), y.stride(0), _p(idx), _p(wts), _p(planes), planes.stride(0), T * top,
+                                  top, n_experts, width, _stream()), "moe_identity")

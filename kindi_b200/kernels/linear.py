@@ -73,3 +73,14 @@ def gate_up_swiglu(ctx, y: torch.Tensor, wgu: torch.Tensor, group: int, f: int, 
     gu = rows_or_planes(ctx, y, wgu, out_dtype)
     K.swiglu(gu, h, group, act)
     return h
+
+
+def gate_up_glu_clamp(ctx, y: torch.Tensor, wgu: torch.Tensor, group: int, f: int, out_dtype: torch.dtype,
+                      limit: float, alpha: float) -> torch.Tensor:
+    """``g' sigmoid(alpha g') (u' + 1)`` with ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)`` and
+    ``[g | u] = y @ wgu^T`` (``wgu`` as ``join_gate_up`` made it): the product as rows or 32-bit planes, then the
+    kernel of the clamped unit"""
+    h = torch.empty((y.shape[0], f), dtype=out_dtype, device=y.device)
+    gu = rows_or_planes(ctx, y, wgu, out_dtype)
+    K.glu_clamp(gu, h, group, limit, alpha)
+    return h

@@ -3,3 +3,4 @@ from . import nanbeige      # noqa: F401
 from . import vozinex       # noqa: F401
 from . import nilatar       # noqa: F401
 from . import medodra       # noqa: F401
+from . import luzerax       # noqa: F401

@@ -2,5 +2,5 @@
 that arranges them in a layer, and heads. Importing this package registers the built-in kinds."""
 from .base import (Block, Branch, Embedding, FeedForward, Head, KVNeed, Mixer, Norm, Part, PositionEncoding, StateNeed,
                    StepContext, WeightView)
-from . import embedding, norm, rope, attention, latent_attention, linear_attention, gated_delta, min_gru, sigmoid_attention, parallel_mixers, mlp, moe, block, head      # noqa: F401  (they register themselves)
+from . import embedding, norm, rope, attention, headnorm_attention, latent_attention, linear_attention, gated_delta, min_gru, sigmoid_attention, parallel_mixers, mlp, moe, block, head      # noqa: F401  (they register themselves)
 from .rope import RotationEncoding                                     # noqa: F401

@@ -16,6 +16,7 @@ import torch
 
 from ..config.registry import part_class, register_part
 from ..config.spec import PartSpec
+from ..kernels import lib as K
 from .base import Block, Branch, StepContext, WeightView
 
 _DEFAULT_NAMES = {"norm1": "input_layernorm.", "mixer": "self_attn.", "norm2": "post_attention_layernorm.",
@@ -134,5 +135,58 @@ class ParallelBlock(PreNormBlock):
         return Branch(planes, self.mult)
 
 
+class PostNormBlock(PreNormBlock):
+    """the norm sits on each sub-layer's OUTPUT and the sub-layers read the residual stream itself:
+    ``x += ls1 * norm1(mixer(x))``, then ``x += ls2 * norm2(feed_forward(x))`` (``layer_scale`` as in the pre-norm
+    block; without it the factor is one). The norms must be RMS norms (they are given as parts so that their eps and
+    the gains' names are parameters; the block reads ``weight`` and ``eps`` of them). One kernel sums a branch's
+    planes, normalises, scales, adds into the 32-bit stream and writes the stream in the run dtype for the next
+    sub-layer to read; the block therefore returns no pending branch, and hands the run-dtype rows of ITS output to
+    the next block of its kind through the step's scratch (a block of another kind, or the final norm, reads the
+    32-bit stream)."""
+
+    def __init__(self, spec, width, weights: WeightView, *, dtype, device):
+        super().__init__(spec, width, weights, dtype=dtype, device=device)
+        for n in (self.norm1, self.norm2):
+            if n is not None and not (hasattr(n, "weight") and hasattr(n, "eps") and not hasattr(n, "bias")):
+                raise ValueError("a post-norm block takes RMS norms")
+        for sc, n in ((self.scale1, self.norm1), (self.scale2, self.norm2)):
+            if sc is not None and sc.dtype != n.weight.dtype:
+                raise ValueError("layer scale and norm gains of %s are stored in different dtypes" % weights.prefix)
+
+    def _rows(self, ctx: StepContext, x):
+        """the stream in the run dtype: what the block before left for this step, else a copy made now"""
+        y = ctx.scratch.pop(("stream rows", x.data_ptr()), None)
+        if y is not None:
+            return y
+        if self.dtype == torch.float32:
+            return x
+        y = torch.empty(x.shape, dtype=self.dtype, device=x.device)
+        K.cast_rows(x, y)
+        return y
+
+    def _add(self, ctx: StepContext, x, branch: Branch, norm, scale):
+        if branch.scale is not None:
+            raise NotImplementedError("a branch with a scale of its own inside a post-norm block")
+        y = x if self.dtype == torch.float32 else torch.empty(x.shape, dtype=self.dtype, device=x.device)
+        K.postnorm_add(x, branch.parts, branch.bias, norm.weight, scale, norm.eps,
+                       None if self.dtype == torch.float32 else y)
+        return y
+
+    def forward(self, ctx: StepContext, x, pending: Optional[Branch]) -> Optional[Branch]:
+        if pending is not None:
+            # a block of another kind ran before: its branch joins the stream as it is
+            if pending.scale is not None:
+                raise NotImplementedError("a scaled pending branch in front of a post-norm block")
+            K.residual_add(x, pending.with_bias_plane().parts, None)
+        y = self._rows(ctx, x)
+        y = self._add(ctx, x, self.mixer.forward(ctx, y), self.norm1, self.scale1)
+        if self.feed_forward is not None:
+            y = self._add(ctx, x, self.feed_forward.forward(ctx, y), self.norm2, self.scale2)
+        ctx.scratch[("stream rows", x.data_ptr())] = y
+        return None
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "postnorm", PostNormBlock)
 register_part("block", "parallel", ParallelBlock)

@@ -17,6 +17,15 @@ Further options, all parameters:
   ones (the order of the logits is the order of their sigmoids, so the pick is the same).
 * ``weight_on`` = ``input`` (gated experts): the weight multiplies the expert's input, ``expert(w y)``, which is
   ``W_down (act(w g) * (w u))`` with ``g = W_gate y``, ``u = W_up y``.
+* ``score`` = ``softmax_all``: the scores are the softmax over ALL router outputs. The choice goes by score +
+  ``correction`` (a tensor suffix, one number per output, or None), the weights by the scores alone, divided by the
+  chosen ones' sum. ``groups`` (``{"count", "keep"}``): the outputs form ``count`` equal groups of neighbours, a
+  group's value is its largest choice score, and only outputs of the ``keep`` best groups can be chosen.
+* ``identity`` (n): the router has ``n_experts + n`` outputs (groups are formed over all of them); the last n are
+  experts without tensors whose output is their input, times the weight.
+* ``activation`` = ``glu_clamp`` (gated experts; ``limit``, ``alpha`` default 1.702): an expert is
+  ``W_down (g' sigmoid(alpha g') (u' + 1))`` with ``g' = min(W_gate y, limit)``, ``u' = clamp(W_up y, -limit, limit)``.
+  A shared expert may have the same activation with a limit of its own (``shared.limit``).
 * ``shared`` (``{"intermediate", "activation", "names": {gate, up, down}, "row_gate": suffix or None}``): a gated
   feed-forward that every row passes through, added as one more plane; with ``row_gate`` (a ``[1, width]`` tensor)
   it is multiplied by ``sigmoid(W_sg y)``, one number per row, whose logit rides in the router's product.
@@ -54,9 +63,12 @@ class MixtureOfExperts(FeedForward):
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
         E, top, f = cls._sizes(spec)
         n = cls._names(spec)
-        out = {n["router"]: (E, width)}
+        n_out = E + int(spec.get("identity") or 0)
+        out = {n["router"]: (n_out, width)}
         if spec.get("router_bias", True):
             out[n["router_bias"]] = (E,)
+        if spec.get("correction"):
+            out[spec["correction"]] = (n_out,)
         for e in range(E):
             out[n["up"] % e] = (f, width)
             out[n["down"] % e] = (width, f)
@@ -87,8 +99,12 @@ class MixtureOfExperts(FeedForward):
         if not (1 <= self.top <= self.E):
             raise ValueError("top_k %d must lie between 1 and n_experts %d" % (self.top, self.E))
         self.act = str(spec.get("activation", "relu2"))
-        if self.act not in K.ACT:
-            raise ValueError("unknown activation %r; known: %s" % (self.act, ", ".join(sorted(K.ACT))))
+        if self.act not in K.ACT and not (self.act == "glu_clamp" and spec.get("gated")):
+            raise ValueError("unknown activation %r; known: %s, and glu_clamp for gated experts"
+                             % (self.act, ", ".join(sorted(K.ACT))))
+        self.act_params = (float(spec["limit"]), float(spec.get("alpha", 1.702))) if self.act == "glu_clamp" else None
+        self.n_identity = int(spec.get("identity") or 0)
+        self.n_out = self.E + self.n_identity
         n = self._names(spec)
         self.wr = weights(n["router"])
         self.br = weights(n["router_bias"]).to(torch.float32).contiguous() if spec.get("router_bias", True) else None
@@ -99,8 +115,32 @@ class MixtureOfExperts(FeedForward):
         self.gated = bool(spec.get("gated"))
         self.score = str(spec.get("score") or "softmax")
         self.weight_on = str(spec.get("weight_on") or "output")
-        if self.score not in K.MOE_SCORE:
-            raise ValueError("unknown router score %r; known: %s" % (self.score, ", ".join(sorted(K.MOE_SCORE))))
+        if self.score not in K.MOE_SCORE and self.score != "softmax_all":
+            raise ValueError("unknown router score %r; known: %s, softmax_all"
+                             % (self.score, ", ".join(sorted(K.MOE_SCORE))))
+        self.correction = None
+        self.groups = (1, 1)
+        if self.score == "softmax_all":
+            if self.br is not None:
+                raise ValueError("a router that scores over all its outputs takes a correction, not a bias")
+            if spec.get("correction"):
+                self.correction = weights(spec["correction"]).to(torch.float32).contiguous()
+            g = spec.get("groups") or {}
+            self.groups = (int(g.get("count", 1)), int(g.get("keep", g.get("count", 1))))
+            if self.groups[0] < 1 or self.n_out % self.groups[0] or not (1 <= self.groups[1] <= self.groups[0]):
+                raise ValueError("%d router outputs do not form %d equal groups of which %d are kept"
+                                 % (self.n_out, self.groups[0], self.groups[1]))
+            if self.top > self.groups[1] * (self.n_out // self.groups[0]):
+                raise ValueError("top_k %d exceeds the %d outputs of the kept groups"
+                                 % (self.top, self.groups[1] * (self.n_out // self.groups[0])))
+            if self.weight_on != "output":
+                raise ValueError("a router that scores over all its outputs weighs the experts' outputs")
+            pad = -self.n_out % 8           # (the products take row counts that are multiples of eight)
+            if pad:
+                self.wr = torch.cat([self.wr, torch.zeros((pad, width), dtype=self.wr.dtype, device=self.wr.device)])
+                self.wr = self.wr.contiguous()
+        elif self.n_identity or spec.get("correction") or spec.get("groups"):
+            raise ValueError("identity experts, a correction and groups belong to the score softmax_all")
         if self.weight_on not in ("output", "input") or (self.weight_on == "input" and not self.gated):
             raise ValueError("weight_on is 'output', or 'input' for gated experts; found %r" % self.weight_on)
         if self.gated:
@@ -117,7 +157,10 @@ class MixtureOfExperts(FeedForward):
             act = str(sh.get("activation") or "silu")
             wgu, group = L.join_gate_up(weights(sn["gate"]), weights(sn["up"]))
             self.shared = (wgu, group, int(sh["intermediate"]), act, weights(sn["down"]))
+            self.shared_params = (float(sh["limit"]), float(sh.get("alpha", 1.702))) if act == "glu_clamp" else None
             self.row_gate = bool(sh.get("row_gate"))
+            if self.row_gate and self.score == "softmax_all":
+                raise NotImplementedError("a row gate beside a router that scores over all its outputs")
             if self.row_gate:
                 # the gate's logit is one more row of the router's product (zero rows fill up to a multiple of eight)
                 rows = [self.wr, weights(sh["row_gate"]).to(self.wr.dtype)]
@@ -126,7 +169,27 @@ class MixtureOfExperts(FeedForward):
                     rows.append(torch.zeros((pad, width), dtype=self.wr.dtype, device=self.wr.device))
                 self.wr = torch.cat(rows, dim=0).contiguous()
 
+    def _forward_all(self, ctx: StepContext, y: torch.Tensor) -> torch.Tensor:
+        """the planes of a router that scores over all its outputs: pick inside the kept groups, the experts'
+        grouped products, and the rows of picks that name an identity expert"""
+        logits = L.linear(ctx, y, self.wr, torch.float32)
+        idx, wts = K.moe_route(logits, self.correction, self.n_out, self.top, self.groups[0], self.groups[1])
+        planes = M.experts(ctx, y, idx, wts, self.wup, self.wdown, self.top, self.act, self.dtype, gated=self.gated,
+                           act_params=self.act_params)
+        K.moe_identity(y, idx, wts, planes, self.E)
+        return planes
+
     def forward(self, ctx: StepContext, y: torch.Tensor) -> Branch:
+        if self.score == "softmax_all":
+            planes = self._forward_all(ctx, y)
+            if self.shared is None:
+                return Branch(planes)
+            wgu, group, fs, act, wd = self.shared
+            if act == "glu_clamp":
+                h = L.gate_up_glu_clamp(ctx, y, wgu, group, fs, self.dtype, *self.shared_params)
+            else:
+                h = L.gate_up_swiglu(ctx, y, wgu, group, fs, self.dtype, act)
+            return Branch(torch.cat([planes, L.planes(ctx, h, wd)], dim=0))
         out = M.feed_forward(ctx, y, self.wr, self.br, self.wup, self.wdown, self.top, self.act, self.dtype,
                              score=self.score, gated=self.gated, weight_on=self.weight_on,
                              n_experts=self.E if self.shared is not None and self.row_gate else None)

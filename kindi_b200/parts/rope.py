@@ -79,6 +79,7 @@ class Rotary(RotationEncoding):
             raise ValueError("pairing must be 'half' or 'interleaved', found %r" % self.pairing)
         f, self.mult = yarn_frequencies(self.base, self.rotary_dim, spec.get("scaling"))
         self.inv_freq = f.to(torch.float32).to(device)
+        self.inv_freq64 = f.to(device)          # for kernels of the true 32-bit path that take their angles in 64-bit
         self.angles_key = ("rotary", self.base, self.rotary_dim) if spec.get("scaling") is None else None
 
 
