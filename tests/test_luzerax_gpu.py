@@ -1,0 +1,495 @@
+"""The Luzerax architecture on the GPU against the plain implementation (``plain_luzerax``): each mechanism's kernel
+alone, then whole models of five small configurations through the engine's step function, its cache and its
+generation loop, in true 32-bit and in bfloat16.
+
+The models carry a planted key (``tiny_luzerax.make_model``): a probe token's attention rests on one needle token, so a
+dropped key, a page of another sequence or a slot's old content changes a probe's logits by many times the tolerance;
+routers are decisive and their corrections change picks. The 32-bit runs are the sharp ones for everything else
+(rotation, norms, temperature, the differential combine, scales).
+"""
+import json
+import os
+import random
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_luzerax as PL
+import tiny
+import tiny_luzerax as TL
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {"float32": 3e-5, "bfloat16": 6e-2}
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def K():
+    from kindi_b200.kernels import lib
+    lib.load()
+    return lib
+
+
+def _status():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+def _rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / (b.abs().max() + 1e-30))
+
+
+def _ctx(T, tdt, fast, **kw):
+    from kindi_b200.parts.base import StepContext
+    base = dict(T=T, B=1, tok=None, pos=None, seq=None, slot=None, q_start=None, kv_len=None, h_slot=None,
+                h_q_start=None, h_kv_len=None, decode=False, max_q=T, max_kv=T, dtype=tdt, device=torch.device("cuda"),
+                status=_status(), fast=fast)
+    base.update(kw)
+    return StepContext(**base)
+
+
+# ------------------------------------------------------------------------------------------- kernels alone
+@pytest.mark.parametrize("T,E,planes,ydtype,scaled,biased", [
+    (1, 64, 1, "float32", True, False), (5, 200, 3, "float32", False, True), (33, 72, 1, "bfloat16", True, False),
+    (3, 4100, 2, "float32", True, False), (200, 256, 9, "bfloat16", True, True), (70, 13, 2, "bfloat16", False, False),
+    (9, 16384, 1, "bfloat16", True, False)])
+def test_norm_on_a_branch_then_add(K, T, E, planes, ydtype, scaled, biased):
+    """x += ls * (w * rms(sum of the planes)); the stream in the run dtype beside it"""
+    g = torch.Generator().manual_seed(T * 1000 + E)
+    tdt = DT[ydtype]
+    x = torch.randn(T, E, generator=g) * 2
+    d = torch.randn(planes, T, E, generator=g) * 3
+    w = (torch.randn(E, generator=g) * 0.3 + 1).to(tdt)
+    ls = (torch.randn(E, generator=g) * 0.5 + 1).to(tdt) if scaled else None
+    bias = torch.randn(E, generator=g) if biased else None
+    v = d.double().sum(0) + (bias.double() if biased else 0.0)
+    want = x.double() + PL.rms(v, 1e-5) * w.double() * (ls.double() if scaled else 1.0)
+    xd = x.cuda()
+    y = torch.full((T, E), float("nan"), dtype=tdt, device="cuda") if ydtype == "bfloat16" else None
+    K.postnorm_add(xd, d.cuda(), bias.cuda() if biased else None, w.cuda(), ls.cuda() if scaled else None, 1e-5, y)
+    assert _rel(xd, want) < 2e-6
+    if y is not None:
+        assert torch.equal(y.cpu(), xd.cpu().to(tdt))
+        z = torch.empty_like(y)
+        K.cast_rows(xd, z)
+        assert torch.equal(z, y)
+
+
+def _scatter_table(lengths, seed, extra=3):
+    rng = random.Random(seed)
+    n_blocks = [-(-n // 64) for n in lengths]
+    n_pages = sum(n_blocks) + extra
+    order = list(range(n_pages))
+    rng.shuffle(order)
+    table = torch.full((len(lengths), max(n_blocks) + 1), -1, dtype=torch.int32)
+    at = 0
+    for s, nb in enumerate(n_blocks):
+        for b in range(nb):
+            table[s, b] = order[at]
+            at += 1
+    return table, n_pages
+
+
+@pytest.mark.parametrize("dtype,planes", [("float32", 1), ("float32", 3), ("bfloat16", 1), ("bfloat16", 4)])
+@pytest.mark.parametrize("nh,nkv,hd,dim,rot,when,gains,coef,every", [
+    (4, 2, 16, 16, 8, "after", False, 0.0, 1), (6, 2, 64, 64, 64, "after", False, 0.0, 1),
+    (8, 4, 128, 48, 0, "before", True, 0.3, 7), (5, 5, 64, 24, 6, "before", True, 1.5, 1),
+    (3, 1, 24, 24, 24, "none", False, 0.4, 100000), (2, 1, 264, 260, 130, "after", True, 0.0, 1)])
+def test_head_norm_rotation_temperature_and_store(K, dtype, planes, nh, nkv, hd, dim, rot, when, gains, coef, every):
+    """every query and key head through its own norm, the rotation and the temperature; queries out, keys and values
+    into scattered pages at positions that cross page borders; heads narrower than the cache's head size"""
+    g = torch.Generator().manual_seed(nh * 100 + hd + rot)
+    tdt = DT[dtype]
+    starts, lens = [0, 61, 700], [3, 70, 5]
+    T = sum(lens)
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)])
+    seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)])
+    n_all = (nh + 2 * nkv) * hd
+    a = torch.zeros(planes, T, nh + 2 * nkv, hd)
+    a[..., :dim] = torch.randn(planes, T, nh + 2 * nkv, dim, generator=g)
+    a = a.view(planes, T, n_all)
+    if dtype == "bfloat16" and planes == 1:
+        xin = a[0].to(tdt)                                   # rows in the run dtype
+        src = xin.float().unsqueeze(0)
+    else:
+        xin = a if planes > 1 else a[0]                      # 32-bit planes (into either run dtype) or 32-bit rows
+        src = a
+    gq = torch.zeros(hd)
+    gk = torch.zeros(hd)
+    gq[:dim] = torch.randn(dim, generator=g) * 0.3 + 1
+    gk[:dim] = torch.randn(dim, generator=g) * 0.3 + 1
+    f64 = 10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1))
+    # the plain result: rotate-half on the first `rot` elements (the interleaved pairing of the plain model, seen
+    # through the permutation evens-first)
+    rows = src.double().sum(0).view(T, nh + 2 * nkv, hd)
+    qk = rows[:, :nh + nkv].clone()
+
+    def norm(v):
+        out = v / torch.sqrt((v * v).sum(-1, keepdim=True) / dim + 1e-5)
+        if gains:
+            out = torch.cat([out[:, :nh] * gq.double(), out[:, nh:] * gk.double()], dim=1)
+        return out
+
+    def rotate(v):
+        if rot == 0:
+            return v
+        perm = list(range(0, rot, 2)) + list(range(1, rot, 2))
+        inter = torch.empty_like(v[..., :rot])
+        inter[..., perm] = v[..., :rot]                      # element i of the half layout is element perm[i] interleaved
+        full = torch.cat([inter, v[..., rot:]], dim=-1)
+        out = torch.empty_like(full)
+        for b, (s, n) in enumerate(zip(starts, lens)):
+            sel = seq == b
+            pad = torch.zeros(s + n, full.shape[1], full.shape[2], dtype=torch.float64)
+            pad[s:] = full[sel]
+            out[sel] = PL.rotate_interleaved(pad, 10000.0, rot)[s:]
+        return torch.cat([out[..., :rot][..., perm], out[..., rot:]], dim=-1)
+
+    if when == "before":
+        qk = rotate(norm(qk))
+    elif when == "after":
+        qk = norm(rotate(qk))
+    else:
+        qk = rotate(qk)
+    temp = torch.tensor([1.0 + coef * np.log((int(p) + 1) // every + 1) for p in pos], dtype=torch.float64)
+    want_q = qk[:, :nh] * temp.view(T, 1, 1)
+    want_k, want_v = qk[:, nh:], rows[:, nh + nkv:]
+    table, n_pages = _scatter_table([s + n for s, n in zip(starts, lens)], seed=hd)
+    pool = torch.full((n_pages, 2, nkv, 64, hd), 7.0, dtype=tdt)
+    qout = torch.full((T, nh * hd + 8), float("nan"), dtype=tdt, device="cuda")
+    st = _status()
+    xin = xin.cuda()
+    poold = pool.cuda()
+    K.headnorm_rope_store(xin, qout, gq.cuda() if gains else None, gk.cuda() if gains else None, 1e-5, dim, when,
+                          f64.float().cuda() if rot else None, f64.cuda() if rot else None, rot, coef, every,
+                          pos.int().cuda(), seq.int().cuda(), torch.arange(3, dtype=torch.int32, device="cuda"), nh,
+                          nkv, nkv, hd, poold, table.cuda(), n_pages, st)
+    assert int(st.item()) == 0
+    tol = 2e-5 if dtype == "float32" else 6e-3
+    assert _rel(qout[:, :nh * hd].view(T, nh, hd), want_q) < tol
+    got = poold.cpu()
+    for t in range(T):
+        page, at = int(table[int(seq[t]), int(pos[t]) // 64]), int(pos[t]) % 64
+        assert _rel(got[page, 0, :, at], want_k[t]) < tol and _rel(got[page, 1, :, at], want_v[t]) < tol
+        got[page, :, :, at] = 7.0
+    assert bool((got == 7.0).all())                          # nothing else was written
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,H,r,hd,vd,lam", [(1, 4, 2, 16, 16, 0.8), (37, 6, 3, 64, 40, -0.3), (5, 3, 1, 128, 128, 1.7),
+                                             (300, 8, 8, 24, 10, 0.55)])
+def test_differential_combine(K, dtype, T, H, r, hd, vd, lam):
+    g = torch.Generator().manual_seed(T + H)
+    tdt = DT[dtype]
+    a = torch.randn(T, H // r, 2, r, hd, generator=g).to(tdt)
+    o = a[:, :, 0, :, :vd].double() - lam * a[:, :, 1, :, :vd].double()
+    want = torch.zeros(T, H, hd, dtype=torch.float64)
+    want[..., :vd] = (PL.rms(o, 1e-5) * 0.4).reshape(T, H, vd)
+    out = torch.full((T, H * hd), float("nan"), dtype=tdt, device="cuda")
+    K.diff_combine(a.reshape(T, -1).cuda(), out, H, r, hd, vd, lam, 1e-5, 0.4)
+    assert _rel(out.view(T, H, hd), want) < (2e-6 if dtype == "float32" else 6e-3)
+
+
+@pytest.mark.parametrize("dtype,planes", [("float32", 1), ("bfloat16", 1), ("bfloat16", 3)])
+def test_gate_per_head(K, dtype, planes):
+    g = torch.Generator().manual_seed(planes)
+    tdt = DT[dtype]
+    T, H, hd = 19, 5, 24
+    a = torch.randn(T, H, hd, generator=g).to(tdt)
+    z = torch.randn(planes, T, 8, generator=g) * 2
+    zin = z if planes > 1 else z[0].to(tdt)
+    want = a.double() * PL.sigmoid(zin.double().sum(0) if planes > 1 else zin.double())[:, :H, None]
+    out = torch.empty(T, H * hd, dtype=tdt, device="cuda")
+    K.head_gate_mul(a.view(T, -1).cuda(), zin.cuda(), out, hd)
+    assert _rel(out.view(T, H, hd), want) < (2e-6 if dtype == "float32" else 6e-3)
+
+
+@pytest.mark.parametrize("n,top,groups,keep", [(4, 2, 1, 1), (16, 4, 4, 2), (8, 2, 4, 3), (6, 2, 3, 1), (12, 3, 3, 2),
+                                               (8, 1, 2, 2), (96, 8, 8, 3), (256, 6, 32, 5), (33, 5, 1, 1)])
+def test_router_pick_within_groups(K, n, top, groups, keep):
+    """softmax over all outputs, the correction in the choice but not in the weights, groups by their best member,
+    weights over the chosen ones' sum; corrections are wide enough that they change picks and make choice scores
+    negative"""
+    g = torch.Generator().manual_seed(n * 7 + top)
+    T = 70
+    z = torch.randn(T, n + 3, generator=g) * 2
+    corr = torch.randn(n, generator=g) * 0.2
+    idx, wts = K.moe_route(z.cuda(), corr.cuda(), n, top, groups, keep)
+    idx, wts = idx.cpu(), wts.cpu()
+    changed = 0
+    for t in range(T):
+        chosen, w = PL.route(z[t, :n].double(), corr.double(), top, groups, keep)
+        assert idx[t].tolist() == chosen, (t, idx[t].tolist(), chosen)
+        assert np.allclose(wts[t].numpy(), w, rtol=2e-5, atol=1e-7)
+        changed += chosen != PL.route(z[t, :n].double(), torch.zeros(n, dtype=torch.float64), top, groups, keep)[0]
+    assert changed > 0
+
+
+@pytest.mark.parametrize("dtype,fast", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+@pytest.mark.parametrize("T,width,E,ident,top,groups,keep,ff,shared", [
+    (1, 64, 4, 0, 2, 1, 1, 24, None), (9, 128, 14, 2, 4, 4, 2, 32, 48), (70, 72, 5, 1, 2, 3, 1, 20, 12),
+    (300, 256, 6, 2, 2, 4, 3, 64, None), (40, 160, 5, 3, 1, 2, 2, 64, 32)])
+def test_experts_with_identity_and_the_clamped_unit(K, dtype, fast, T, width, E, ident, top, groups, keep, ff, shared):
+    """the feed-forward part alone: router, picks, clamped experts (limits that bite on both sides), identity experts,
+    the shared expert with a limit of its own"""
+    from kindi_b200.config.registry import part_class
+    from kindi_b200.config.spec import PartSpec
+    from kindi_b200.parts.base import WeightView
+    g = torch.Generator().manual_seed(T + width + E)
+    tdt = DT[dtype]
+    f = {"kind": "moe", "expert": {"ff": ff, "limit": 0.6},
+         "router": {"experts": E, "identity": ident, "top": top, "groups": {"count": groups, "keep": keep}},
+         "shared": None if shared is None else {"ff": shared, "limit": 0.3}}
+    t = {"router": torch.randn(E + ident, width, generator=g) * 0.4, "correction": torch.randn(E + ident, generator=g) * 0.1}
+    for e in list(range(E)) + (["s"] if shared else []):
+        p, n = ("shared." if e == "s" else "e%d." % e), (shared if e == "s" else ff)
+        t[p + "gate"], t[p + "up"] = (torch.randn(n, width, generator=g) * 0.15 for _ in range(2))
+        t[p + "down"] = torch.randn(width, n, generator=g) * 0.15
+    t = {k: v.to(tdt) for k, v in t.items()}
+    y = torch.randn(T, width, generator=g).to(tdt)
+    want = PL.expert_feed_forward({k: v for k, v in t.items()}, "", f, y.double())
+    spec = PartSpec("moe", {
+        "n_experts": E, "top_k": top, "intermediate": ff, "gated": True, "activation": "glu_clamp", "limit": 0.6,
+        "score": "softmax_all", "router_bias": False, "correction": "correction", "identity": ident,
+        "groups": {"count": groups, "keep": keep},
+        "shared": None if shared is None else {"intermediate": shared, "activation": "glu_clamp", "limit": 0.3,
+                                               "names": {"gate": "shared.gate", "up": "shared.up", "down": "shared.down"}},
+        "names": {"router": "router", "gate": "e%d.gate", "up": "e%d.up", "down": "e%d.down"}})
+    part = part_class("feed_forward", "moe")(spec, width, WeightView({k: v.cuda() for k, v in t.items()}), dtype=tdt,
+                                             device=torch.device("cuda"))
+    ctx = _ctx(T, tdt, fast)
+    got = part.forward(ctx, y.cuda()).parts.sum(0)
+    assert int(ctx.status.item()) == 0
+    # (a row whose two best choice scores lie closer than the 16-bit rounding of the logits may pick otherwise)
+    err = (got.double().cpu() - want).abs().max(dim=1).values / want.abs().max()
+    bad = int((err > (3e-5 if dtype == "float32" else 2e-2)).sum())
+    assert bad <= (0 if dtype == "float32" else T // 30), (bad, float(err.max()))
+
+
+# ------------------------------------------------------------------------------------------- whole models
+def _plain(folder, reqs):
+    cfg, w = PL.load_model(folder)
+    return {rid: PL.forward(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+
+
+def _compare(got, reqs, want, tol, what):
+    for rid, toks in reqs.items():
+        mine = np.stack([got[(rid, i)] for i in range(len(toks))])
+        err = tiny.rel_err(mine, want[rid])
+        row = int(np.argmax(np.max(np.abs(mine - want[rid]), axis=1)))
+        assert err <= tol, "%s %s: %.3g at position %d of %d" % (what, rid, err, row, len(toks))
+
+
+def _edge_requests(raw, seed, L=200):
+    """requests whose needle stands at the places that matter - the first positions, at a page border, far back, right
+    before the probes - with probes over the last positions; and the shortest sequences there are"""
+    rng = random.Random(seed)
+    vocab = raw["vocab"]
+    reqs = {}
+    for p in (0, 1, 63, 64, 127, 128, L - 8):
+        reqs["n%d" % p] = TL.needle_request(vocab, L, p, list(range(L - 6, L)), rng)
+    reqs["one"] = [rng.randrange(5, vocab)]
+    reqs["two"] = [rng.randrange(5, vocab), TL.PROBE]
+    return reqs
+
+
+def _engine(folder, steps, dtype, **kw):
+    from kindi_b200.engine.engine import Engine
+    return Engine(folder, ctx=tiny.max_live_tokens(steps) + 64, dtype=dtype,
+                  max_batch=max(len(s["entries"]) for s in steps), **kw)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(TL.TINY))
+def test_whole_prompts_and_token_by_token(tmp_path, name, dtype):
+    """every request whole in one step, then again with its last 40 tokens one by one (the temperature steps up under
+    decoded tokens, the needle lies pages back), in the same engine, slots and pages"""
+    raw = TL.TINY[name][0]
+    folder = TL.make_model(tmp_path, name, dtype)
+    reqs = _edge_requests(raw, seed=3)
+    want = _plain(folder, reqs)
+    steps = tiny.trace_whole(reqs)
+    later = tiny.trace_last_n(reqs, 40)
+    for s in later:
+        s["step"] += len(steps)
+    eng = _engine(folder, steps + later, dtype)
+    out = str(tmp_path / "out")
+    tiny.run_replay(eng, steps, out)
+    _compare(tiny.collect(out, steps, raw["vocab"]), reqs, want, TOL[dtype], "%s %s whole" % (name, dtype))
+    tiny.run_replay(eng, later, out)
+    _compare(tiny.collect(out, later, raw["vocab"]), reqs, want, TOL[dtype], "%s %s decoded" % (name, dtype))
+    eng.check_status()
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0 and all(g.pages.pool.n_held == 0 for g in eng.cache.groups)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_prompts_in_portions(tmp_path, name, dtype):
+    """a prompt cut into portions of 2, 3, 31, 64 and 65 tokens, and a step limit that cuts it inside the engine: the
+    logits are those of the whole prompt"""
+    from kindi_b200.engine.engine import Engine
+    raw = TL.TINY[name][0]
+    folder = TL.make_model(tmp_path, name, dtype)
+    reqs = {k: v for k, v in _edge_requests(raw, seed=4).items() if k in ("n0", "n64", "two")}
+    want = _plain(folder, reqs)
+    for portion in (2, 3, 31, 64, 65):
+        steps = []
+        for rid, toks in reqs.items():
+            for a in range(0, len(toks), portion):
+                part = toks[a:a + portion]
+                steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": part,
+                                                               "want": list(range(len(part)))}],
+                              "end": [rid] if a + portion >= len(toks) else []})
+        eng = _engine(folder, steps, dtype)
+        out = str(tmp_path / ("out%d" % portion))
+        tiny.run_replay(eng, steps, out)
+        eng.check_status()
+        _compare(tiny.collect(out, steps, raw["vocab"]), reqs, want, TOL[dtype], "%s %s by %d" % (name, dtype, portion))
+    steps = tiny.trace_whole(reqs)
+    eng = Engine(folder, ctx=tiny.max_live_tokens(steps) + 64, dtype=dtype, max_batch=2, max_step_tokens=64)
+    out = str(tmp_path / "outcut")
+    tiny.run_replay(eng, steps, out)
+    _compare(tiny.collect(out, steps, raw["vocab"]), reqs, want, TOL[dtype], "%s %s cut inside" % (name, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(TL.TINY))
+def test_unequal_batches_and_reused_slots(tmp_path, name, dtype):
+    """batches of unequal requests that start together and are decoded together, shorter ones ending earlier, a
+    second batch in the slots and pages the first gave back: every row as if its request ran alone"""
+    raw = TL.TINY[name][0]
+    folder = TL.make_model(tmp_path, name, dtype)
+    reqs = _edge_requests(raw, seed=6)
+    ids = list(reqs)
+    rng = random.Random(9)
+    decode = {r: min(len(reqs[r]) - 1, rng.choice([0, 3, 9, 30])) for r in ids}
+    half = len(ids) // 2
+    steps = tiny.trace_group({r: reqs[r] for r in ids[:half]}, decode)
+    steps += tiny.trace_group({r: reqs[r] for r in ids[half:]}, decode, first_step=len(steps))
+    want = _plain(folder, reqs)
+    eng = _engine(folder, steps, dtype)
+    out = str(tmp_path / "out")
+    tiny.run_replay(eng, steps, out)
+    eng.check_status()
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0 and all(g.pages.pool.n_held == 0 for g in eng.cache.groups)
+    _compare(tiny.collect(out, steps, raw["vocab"]), reqs, want, TOL[dtype], "%s %s batches" % (name, dtype))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_in_a_batch(tmp_path, dtype):
+    """three requests decoded together for 200 steps (recorded decode steps) across page borders and temperature
+    steps, probes all the way, a needle far back"""
+    raw = TL.TINY["B"][0]
+    folder = TL.make_model(tmp_path, "B", dtype)
+    rng = random.Random(2)
+    reqs = {"a": TL.needle_request(raw["vocab"], 270, 2, list(range(60, 270, 3)), rng),
+            "b": TL.needle_request(raw["vocab"], 250, 69, list(range(100, 250, 2)), rng),
+            "c": TL.needle_request(raw["vocab"], 215, 10, list(range(20, 215, 5)), rng)}
+    steps = tiny.trace_group(reqs, {"a": 200, "b": 200, "c": 200})
+    want = _plain(folder, reqs)
+    eng = _engine(folder, steps, dtype)
+    out = str(tmp_path / "out")
+    tiny.run_replay(eng, steps, out)
+    eng.check_status()
+    assert eng.graph_replays > 150
+    _compare(tiny.collect(out, steps, raw["vocab"]), reqs, want, TOL[dtype], "long %s" % dtype)
+
+
+@pytest.mark.parametrize("dtype,tie", [("float32", 1e-5), ("bfloat16", 2e-2)])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype, tie):
+    from kindi_b200 import Engine
+    raw = TL.TINY[name][0]
+    folder = TL.make_model(tmp_path, name, dtype)
+    cfg, w = PL.load_model(folder)
+    eng = Engine(folder, ctx=2048, dtype=dtype, max_batch=3)
+    prompts = list(tiny.random_requests(raw["vocab"], [5, 9, 1, 80, 13], seed=3).values())
+    res = eng.generate_batch(prompts, temperature=0.0, max_tokens=10, stop_token_ids=())
+    assert res.stats.batches == 2 and eng.cache.slots.n_held == 0
+    for p, got in zip(prompts, res.tokens):
+        assert len(got) == 10
+        seq = list(p)
+        for t in got:
+            z = PL.forward(cfg, w, seq)[-1].numpy()
+            best = int(np.argmax(z))
+            assert t == best or z[best] - z[t] <= tie * np.abs(z).max(), (len(seq), t, best)
+            seq.append(t)
+    eng.cache.check()
+
+
+def test_trace_run_and_command_line_as_programs(tmp_path):
+    folder = TL.make_model(tmp_path, "A", "bfloat16")
+    vocab = TL.LZ_A["vocab"]
+    reqs = tiny.random_requests(vocab, [5, 40], seed=2)
+    steps = tiny.trace_batched(reqs, batch=2, decode=4)
+    out = str(tmp_path / "out")
+    env = dict(os.environ, PYTHONDONTWRITEBYTECODE="1")
+    r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "bfloat16", "--out", out,
+                        "--max-tokens", str(tiny.max_live_tokens(steps))],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = tiny.collect(out, steps, vocab)
+    _compare(got, reqs, _plain(folder, reqs), TOL["bfloat16"], "trace_run")
+    r = subprocess.run([sys.executable, "-m", "kindi_b200", "--model", folder, "--ctx", "512", "generate",
+                        "--prompt-ids", "1,2,3", "--prompt-ids", "9 8", "--temperature", "0", "--max-tokens", "5"],
+                       capture_output=True, text=True, cwd=ROOT, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(l) for l in r.stdout.strip().split("\n")]
+    assert len(lines) == 2 and all(len(l["tokens"]) == 5 for l in lines)
+    r = subprocess.run([sys.executable, "-m", "kindi_b200", "--model", folder, "info"], capture_output=True, text=True,
+                       cwd=ROOT, env=env, timeout=600)
+    assert r.returncode == 0 and "Luzerax" in r.stdout + r.stderr, r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recorded_prompt_steps_and_their_padding_rows(tmp_path, dtype):
+    """short prompt steps are padded to a multiple of 64 rows and replayed from a recording once their shape has come
+    twice: the padding rows store nothing and change no other row; in 32-bit a recorded step gives the bits of an
+    engine that records nothing"""
+    from kindi_b200.engine.batch import StepEntry
+    from kindi_b200.engine.engine import Engine
+    raw = TL.TINY["B"][0]
+    folder = TL.make_model(tmp_path, "B", dtype)
+    cfg, w = PL.load_model(folder)
+    rng = random.Random(9)
+    eng = Engine(folder, ctx=4096, dtype=dtype, max_batch=4)
+    plain_eng = Engine(folder, ctx=4096, dtype=dtype, max_batch=4, cuda_graphs=False)
+
+    def run(e, groups, follow=3):
+        out = []
+        for group in groups:
+            slots = [e.alloc() for _ in group]
+            k = [len(t) - follow for t in group]
+            logits = e.step([StepEntry(s, tuple(t[:n]), (n - 1,)) for s, t, n in zip(slots, group, k)])
+            rows = [[logits[i].cpu().numpy()] for i in range(len(group))]
+            for j in range(follow):
+                lg = e.step([StepEntry(s, (t[n + j],), (0,)) for s, t, n in zip(slots, group, k)])
+                for i in range(len(group)):
+                    rows[i].append(lg[i].cpu().numpy())
+            e.check_status()
+            for s in slots:
+                e.free(s)
+            out.append([np.stack(r) for r in rows])
+        return out
+
+    lengths = [[103], [93], [131], [68], [73], [40, 71], [64, 9], [8, 100], [200]]
+    groups = [[TL.needle_request(raw["vocab"], n, 1, list(range(n - 5, n)), rng) for n in g] for g in lengths]
+    got = run(eng, groups)
+    assert sum(1 for k in eng._graphs if k[0] == "prompt") >= 2 and eng.graph_replays >= 6
+    same = run(plain_eng, groups)
+    for g, mine, other in zip(groups, got, same):
+        for toks, a, b in zip(g, mine, other):
+            want = PL.forward(cfg, w, toks).numpy()[len(toks) - 4:]
+            assert tiny.rel_err(a, want) <= TOL[dtype], (len(toks), tiny.rel_err(a, want))
+            if dtype == "float32":
+                assert np.array_equal(a, b), len(toks)
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
