@@ -142,7 +142,36 @@ def route(z: torch.Tensor, correction: torch.Tensor, top: int, groups: int, keep
     return chosen, [float(s[e]) / total for e in chosen]
 
 
-def expert_feed_forward(t, p: str, f: Mapping, h: torch.Tensor) -> torch.Tensor:
+def route_margin(z: torch.Tensor, correction: torch.Tensor, top: int, groups: int, keep: int,
+                 weight: float = 0.02) -> float:
+    """how far the row is from another pick that would matter: the gap between the last choice score that was taken
+    and the best that was not (experts inside the kept groups, and the groups' own scores), counted only where the
+    experts that would change places hold more than ``weight`` of the chosen ones' scores"""
+    n = z.numel()
+    s = torch.exp(z - z.max())
+    s = s / s.sum()
+    c = s + correction
+    size = n // groups
+    chosen, _ = route(z, correction, top, groups, keep)
+    total = sum(float(s[e]) for e in chosen) + 1e-20
+    order = sorted(range(groups), key=lambda g: (-float(c[g * size:(g + 1) * size].max()), g))
+    margin = float("inf")
+    if keep < groups:
+        last, nxt = order[keep - 1], order[keep]
+        moved = max(float(s[e]) for g in (last, nxt) for e in range(g * size, (g + 1) * size))
+        if moved > weight * total:
+            margin = float(c[last * size:(last + 1) * size].max() - c[nxt * size:(nxt + 1) * size].max())
+    rest = [e for e in range(n) if e // size in order[:keep] and e not in chosen]
+    if rest:
+        k = min(chosen, key=lambda e: float(c[e]))
+        u = max(rest, key=lambda e: float(c[e]))
+        if max(float(s[k]), float(s[u])) > weight * total:
+            margin = min(margin, float(c[k] - c[u]))
+    return margin
+
+
+def expert_feed_forward(t, p: str, f: Mapping, h: torch.Tensor, margins: list = None) -> torch.Tensor:
+    """``margins`` (a list) receives a tensor [T]: every row's ``route_margin``"""
     r = f["router"]
     E, n_id, top = int(r["experts"]), int(r["identity"]), int(r["top"])
     limit = float(f["expert"]["limit"])
@@ -156,13 +185,18 @@ def expert_feed_forward(t, p: str, f: Mapping, h: torch.Tensor) -> torch.Tensor:
                 out[i] += w * h[i]                       # an identity expert
             else:
                 out[i] += w * clamped_expert(t, p + "e%d." % e, h[i:i + 1], limit)[0]
+    if margins is not None:
+        margins.append(torch.tensor([route_margin(z[i], corr, top, int(r["groups"]["count"]), int(r["groups"]["keep"]))
+                                     for i in range(h.shape[0])], dtype=F64))
     if f.get("shared"):
         out = out + clamped_expert(t, p + "shared.", h, float(f["shared"]["limit"]))
     return out
 
 
-def forward(cfg: Mapping, t: Mapping[str, torch.Tensor], tokens: List[int], residuals: list = None) -> torch.Tensor:
-    """logits [T, vocab] of one sequence; ``residuals`` (a list) receives the stream after every layer"""
+def forward(cfg: Mapping, t: Mapping[str, torch.Tensor], tokens: List[int], residuals: list = None,
+            margins: list = None) -> torch.Tensor:
+    """logits [T, vocab] of one sequence; ``residuals`` (a list) receives the stream after every layer, ``margins`` (a
+    list) every routed layer's ``route_margin`` per row"""
     eps = float(cfg["norm"]["eps"])
     x = _w(t, "embed")[torch.tensor(tokens, dtype=torch.long)]
     for i, layer in enumerate(cfg["layers"]):
@@ -171,7 +205,8 @@ def forward(cfg: Mapping, t: Mapping[str, torch.Tensor], tokens: List[int], resi
         x = x + rms(mix(t, p + "mix.", layer["mixer"], x, eps), eps) * _w(t, p + "norm1") * _w(t, p + "ls1")
         f = layer.get("mlp")
         if f is not None:
-            y = dense_feed_forward(t, p + "mlp.", x) if f["kind"] == "dense" else expert_feed_forward(t, p + "mlp.", f, x)
+            y = dense_feed_forward(t, p + "mlp.", x) if f["kind"] == "dense" else \
+                expert_feed_forward(t, p + "mlp.", f, x, margins)
             x = x + rms(y, eps) * _w(t, p + "norm2") * _w(t, p + "ls2")
         if residuals is not None:
             residuals.append(x.clone())

@@ -25,7 +25,7 @@ def test_config_reads_every_size_from_the_nested_keys():
     assert [l.kind for l in cfg.layers] == ["attention", "attention", "attention_2"]
     m = cfg.layers[0].mixer
     assert (m.heads, m.kv_heads, m.dim, m.vdim, m.scale, m.diff, m.temp_coef, m.temp_every) == \
-        (4, 2, 16, 24, 0.5, 0.8, 0.5, 16)
+        (4, 2, 16, 24, 0.5, 0.55, 0.5, 16)
     m = cfg.layers[2].mixer
     assert (m.heads, m.kv_heads, m.dim, m.vdim, m.rot_base, m.rot_dims) == (4, 2, 16, 24, 10000.0, 8)
     f = cfg.layers[0].ff

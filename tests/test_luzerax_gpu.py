@@ -24,7 +24,12 @@ import tiny_luzerax as TL
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-TOL = {"float32": 3e-5, "bfloat16": 6e-2}
+# (bfloat16: with activations stored in 16 bits the typical row of these models lies 1 % of the largest logit away from
+# the 64-bit result, one row in a hundred 3 %, single rows up to 10 %: a layer adds a branch of unit size whatever the
+# branch's own size was, and a differential head amplifies the rounding of its two maps by 1 / (1 - lambda). What the
+# planted key changes is more than 30 %. The 32-bit runs are the sharp ones.)
+TOL = {"float32": 3e-5, "bfloat16": 0.12}
+TYPICAL = 0.03             # bfloat16: the median row of a request
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
@@ -272,17 +277,44 @@ def test_experts_with_identity_and_the_clamped_unit(K, dtype, fast, T, width, E,
 
 
 # ------------------------------------------------------------------------------------------- whole models
+CLOSE_CALL = 0.003          # a pick whose choice scores lie closer than this may fall the other way in bfloat16
+
+
 def _plain(folder, reqs):
+    """{request: (logits, per row: the smallest margin of its routers' picks)}"""
     cfg, w = PL.load_model(folder)
-    return {rid: PL.forward(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+    out = {}
+    for rid, toks in reqs.items():
+        margins = []
+        z = PL.forward(cfg, w, toks, margins=margins).numpy()
+        m = torch.stack(margins).min(dim=0).values.numpy() if margins else np.full(len(toks), np.inf)
+        out[rid] = (z, m)
+    return out
 
 
 def _compare(got, reqs, want, tol, what):
+    """every row within ``tol`` of the plain model's. In bfloat16 the router's logits are products of 16-bit numbers: a
+    row whose pick is a close call on the plain model may pick otherwise (and a later row that rests on it, a probe
+    on a needle, follows), so such rows are left out there - a request whose needle is one, altogether. In 32-bit no
+    row is left out."""
+    sharp = tol < 1e-3
+    n_out = n_all = 0
     for rid, toks in reqs.items():
+        z, margin = want[rid]
         mine = np.stack([got[(rid, i)] for i in range(len(toks))])
-        err = tiny.rel_err(mine, want[rid])
-        row = int(np.argmax(np.max(np.abs(mine - want[rid]), axis=1)))
-        assert err <= tol, "%s %s: %.3g at position %d of %d" % (what, rid, err, row, len(toks))
+        n_all += len(toks)
+        keep = np.ones(len(toks), dtype=bool) if sharp else margin >= CLOSE_CALL
+        if not sharp and TL.NEEDLE in toks and not keep[toks.index(TL.NEEDLE)]:
+            n_out += len(toks)
+            continue
+        n_out += int((~keep).sum())
+        err = np.max(np.abs(mine - z), axis=1) / np.max(np.abs(z))
+        err = np.where(keep, err, 0.0)
+        row = int(np.argmax(err))
+        assert err[row] <= tol, "%s %s: %.3g at position %d of %d" % (what, rid, err[row], row, len(toks))
+        assert sharp or np.median(err) <= TYPICAL, "%s %s: the median row is %.3g off" % (what, rid, np.median(err))
+    assert n_out <= 0.25 * n_all, "%s: %d of %d rows are close calls: the test's routers are not decisive" % (
+        what, n_out, n_all)
 
 
 def _edge_requests(raw, seed, L=200):

@@ -15,6 +15,7 @@ from typing import List
 
 NEEDLE, PROBE = 3, 4            # token ids: the needle's key stands out for every probe's query
 CODE = 3.0                      # the size of the planted embedding features, far above the random ones
+KEPT = 10                       # the stream's first columns keep the token's own features through all layers
 
 
 def _dense(ff):
@@ -46,7 +47,7 @@ def _config(vocab, width, eps, layers):
 # A: small everything; two differential layers in a row; values wider than keys; half of a head rotated; experts in
 #    one group without identity experts or a shared expert; a layer without a feed-forward
 LZ_A = _config(211, 64, 1e-5, [
-    _diff(4, 2, 16, 24, 0.5, 0.8, 0.5, 16, _moe(4, 0, 2, 1, 1, 24, 0.7)),
+    _diff(4, 2, 16, 24, 0.5, 0.55, 0.5, 16, _moe(4, 0, 2, 1, 1, 24, 0.7)),
     _diff(2, 1, 16, 8, 0.45, 0.3, 0.25, 7),
     _rot(4, 2, 16, 24, 0.6, 10000.0, 8, _dense(40))])
 # B: head size 64 (the tensor-core attention kernels run in bfloat16), three query heads per key/value head, whole
@@ -70,7 +71,7 @@ LZ_C = _config(257, 200, 2e-6, [
 LZ_D = _config(131, 72, 1e-5, [
     _rot(5, 5, 24, 10, 0.25, 30000.0, 6, _moe(5, 1, 2, 3, 1, 20, 1.0)),
     _rot(3, 1, 24, 10, 0.2, 100.0, 24, _dense(20)),
-    _diff(3, 3, 10, 24, 0.9, 0.7, 0.3, 5, _moe(5, 1, 2, 3, 1, 20, 1.0, (12, 1.5)))])
+    _diff(3, 3, 10, 24, 0.9, 0.4, 0.3, 5, _moe(5, 1, 2, 3, 1, 20, 1.0, (12, 1.5)))])
 # E: values far wider than keys, one pick a row, more identity experts than the kept groups hold experts, every group
 #    kept, no rotation at all in a rotated layer's configuration (dims 0)
 LZ_E = _config(401, 160, 1e-5, [
@@ -88,9 +89,11 @@ def make_model(tmp_path, name: str, dtype: str = "bfloat16", strength: float = 1
     differential layer) reads column 0 into its last dimension with a weight far above the random ones, and the query
     projections of that group's heads read column 1 into the same dimension: after the heads' norms both are about
     sqrt(dim) in that dimension, and the layer's scale is set so that the score is ``strength``. The value projection
-    reads column 0 with a large weight. The router's rows are scaled up and the correction drawn wide, so that picks
-    are decided and the correction changes them. With plain random weights attention is nearly uniform, and a key that
-    is dropped moves the logits by less than the rounding error of bfloat16."""
+    reads column 0 with a large weight. The routers read nothing but eight further kept columns, which hold features of
+    the token's own of size one: a row's picks then follow from its token with logits of ordinary size, the correction
+    changes them, and the 16-bit rounding of activations cannot (the products of stored numbers are exact in both
+    implementations). Lambda stays within a tenth of ``diff``, and ``diff`` well below one: where both maps see the same few keys (a sequence's first positions) the head is ``(1 - lambda)`` times a value, and 16-bit rounding of the maps' outputs is amplified by ``1 / (1 - lambda)``. With plain random weights attention is nearly
+    uniform, and a key that is dropped moves the logits by less than the rounding error of bfloat16."""
     import torch
     from kindi_b200.config.registry import model_from_config
     from kindi_b200.parts.model import expected_tensors, tensor_inits
@@ -107,10 +110,11 @@ def make_model(tmp_path, name: str, dtype: str = "bfloat16", strength: float = 1
     _, spec = model_from_config(cfg)
     t = random_tensors(expected_tensors(spec), seed, dtype=torch.float32, inits=tensor_inits(spec))
     emb = t["embed"]
+    g = torch.Generator().manual_seed(seed + 1)
     emb[:, 0:2] = 0.0
     emb[NEEDLE, 0] = CODE
     emb[PROBE, 1] = CODE
-    g = torch.Generator().manual_seed(seed + 1)
+    emb[:, 2:KEPT] = torch.randn(emb.shape[0], KEPT - 2, generator=g)
     for i, layer in enumerate(cfg["layers"]):
         m = layer["mixer"]
         p = "l%d.mix." % i
@@ -127,16 +131,32 @@ def make_model(tmp_path, name: str, dtype: str = "bfloat16", strength: float = 1
             for n in ("q.norm", "k.norm"):
                 t[p + n][at] = 1.0
             for n in ("lq1", "lk1", "lq2", "lk2"):
-                t[p + n] = 0.4 * torch.randn(dim, generator=g)
+                t[p + n] = 0.3 * torch.randn(dim, generator=g) / dim ** 0.5
         f = layer["mlp"]
         if f is not None and f["kind"] == "moe":
             q = "l%d.mlp." % i
-            t[q + "router"] = t[q + "router"] * 40.0
-            t[q + "correction"] = 0.15 * torch.randn(t[q + "correction"].shape, generator=g)
-    # no branch writes into the planted columns: what the planted keys and queries read stays the tokens' own
+            t[q + "router"][:] = 0.0
+            t[q + "router"][:, 2:KEPT] = 0.6 * torch.randn(t[q + "router"].shape[0], KEPT - 2, generator=g)
+            t[q + "correction"] = 0.1 * torch.randn(t[q + "correction"].shape, generator=g)
+    # the needle's and the probes' own picks are no close calls (they stand in every request): their kept features are
+    # drawn again until every routed layer picks with a clear gap, also when an identity expert has stretched them
+    from plain_luzerax import route_margin
+    routed = [(t["l%d.mlp.router" % i].double(), t["l%d.mlp.correction" % i].double(), l["mlp"]["router"])
+              for i, l in enumerate(cfg["layers"]) if l["mlp"] is not None and l["mlp"]["kind"] == "moe"]
+    for tok in (NEEDLE, PROBE):
+        for _ in range(500):
+            feat = emb[tok].double()
+            if all(route_margin(wr @ feat * sc, corr, r["top"], r["groups"]["count"], r["groups"]["keep"], 0.0) >= 0.05
+                   for wr, corr, r in routed for sc in (0.7, 1.0, 1.4)):
+                break
+            emb[tok, 2:KEPT] = torch.randn(KEPT - 2, generator=g)
+        else:
+            raise RuntimeError("no features with clear picks found for token %d" % tok)
+    # no branch writes into the kept columns: what the planted keys and queries and the routers read stays the tokens'
+    # own (an identity expert hands them through: that changes their size, not their direction)
     for n in list(t):
         if n.endswith(".mix.o") or n.endswith(".down"):
-            t[n][0:2, :] = 0.0
+            t[n][0:KEPT, :] = 0.0
     tdt = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
     t = {n: v.to(tdt) for n, v in t.items()}
     with open(os.path.join(d, "config.json"), "w") as f:
