@@ -482,6 +482,74 @@ def bench_medodra(a) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- --arch luzerax
+# Layer sizes that resemble real models' (random weights, four layers: rotated attention with a norm and a gate per
+# head, differential attention, and both once more; each with a mixture of clamped gated experts - 14 experts and two
+# identity experts in four groups of which two are kept, three a token, plus a shared expert), each beside the Vozinex
+# design (the closest one: attention layers with routed experts on the same engine) of the same width, heads, head
+# size, expert count and ACTIVE feed-forward size (an expert here has three matrices of two thirds the inner size of
+# Vozinex's two; three picks and the shared expert against Vozinex's four picks), with a window that never closes.
+LUZERAX_IDENTITY, LUZERAX_GROUPS, LUZERAX_KEEP = 2, 4, 2
+
+
+def luzerax_pair(sz: dict):
+    """(Luzerax config, Vozinex config of equal size) at the sizes of VOZINEX_SIZES[.]"""
+    hd = VOZINEX_HEAD
+    ff = sz["ff"] * 2 // 3 // 64 * 64
+    top = sz["top"] - 1
+    mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0},
+           "router": {"experts": sz["experts"] - LUZERAX_IDENTITY, "identity": LUZERAX_IDENTITY, "top": top,
+                      "groups": {"count": LUZERAX_GROUPS, "keep": LUZERAX_KEEP}},
+           "shared": {"ff": ff, "limit": 7.0}}
+    common = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5}
+    rot = {"type": "attention_2", "mixer": dict(common, rot={"base": 500000.0, "dims": hd}), "mlp": mlp}
+    dif = {"type": "attention", "mixer": dict(common, diff=0.6, q_temp={"coef": 0.1, "every": 512}), "mlp": mlp}
+    luz = {"architecture": "Luzerax", "vocab": VOZINEX_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5},
+           "layers": [rot, dif, rot, dif]}
+    voz, _, _ = vozinex_pair(sz)
+    for layer in voz["layers"]:
+        layer["mixer"] = dict(layer["mixer"], mask=None)
+    return luz, voz
+
+
+def bench_luzerax(a) -> int:
+    """prefill and decode throughput of the Luzerax design at three layer sizes, each beside the Vozinex design of
+    equal size, with the device time per kind of launch"""
+    import torch
+    pk = peaks()
+    batch, context, tokens = a.batch, min(a.context, 4096), a.prefill_tokens
+    sizes = [x for x in (a.sizes or "s,m,l").split(",") if x in VOZINEX_SIZES]
+    rows = {}
+    for name in sizes:
+        sz = VOZINEX_SIZES[name]
+        luz, voz = luzerax_pair(sz)
+        ctx = batch * (context + a.steps + a.warmup + 320) + tokens + 64
+        m = luz["layers"][0]["mlp"]
+        row = {"sizes": dict(width=sz["width"], heads=sz["heads"], kv=sz["kv"], head=VOZINEX_HEAD, layers=4,
+                             experts=m["router"]["experts"], identity=LUZERAX_IDENTITY, top=m["router"]["top"],
+                             expert_ff=m["expert"]["ff"], shared_ff=m["shared"]["ff"], vozinex_expert_ff=sz["ff"],
+                             vozinex_top=sz["top"])}
+        for what, cfg in (("luzerax", luz), ("vozinex", voz)):
+            eng = engine_from_config(cfg, ctx, batch)
+            for g in eng.cache.groups:
+                g.pool.normal_(0.0, 1.0)
+            dev_ms, _, launches, _ = bench_decode(eng, batch, context, a.steps, max(3, a.warmup), False)
+            pms = bench_prefill(eng, 3, 5, tokens)
+            kt = kernel_times(eng, batch, context, tokens)
+            row[what] = {"decode_ms": round(dev_ms, 4), "decode_tokens_per_s": round(batch * 1000.0 / dev_ms, 1),
+                         "launches_per_step": launches // a.steps, "prefill_ms": round(pms, 3),
+                         "prefill_tokens_per_s": round(tokens * 1000.0 / pms, 1),
+                         "kernels_us": {k: _grouped(v) for k, v in kt.items()}}
+            del eng
+            torch.cuda.empty_cache()
+        rows[name] = row
+    print(json.dumps({"arch": "luzerax", "what": "prefill and decode of the Luzerax design beside the Vozinex design of "
+                      "equal size (random weights, 4 layers); not the default benchmark",
+                      "batch": batch, "context": context, "prefill_tokens": tokens, "steps": a.steps, "dtype": "bf16",
+                      "peaks": pk, "sizes": rows}))
+    return 0
+
+
 def kernel_times(eng, batch: int, context: int, prefill_tokens: int):
     """device time per kind of launch: one decode step of `batch` sequences at `context` and one prompt pass, each
     issued launch by launch (no recorded graph, launches strictly one after another) with CUDA events around every
@@ -713,11 +781,11 @@ def main(argv=None) -> int:
                          "0.7, top-p 0.8, top-k 20) and report it as e2e_sampled")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
     ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill (for profiling)")
-    ap.add_argument("--arch", default="nanbeige", choices=("nanbeige", "vozinex", "nilatar", "medodra"),
-                    help="vozinex, nilatar, medodra: not the default benchmark but that design at a few layer sizes, "
+    ap.add_argument("--arch", default="nanbeige", choices=("nanbeige", "vozinex", "nilatar", "medodra", "luzerax"),
+                    help="vozinex, nilatar, medodra, luzerax: not the default benchmark but that design at a few layer sizes, "
                          "each beside the closest other decoder of equal size (prefill, decode, device time per kind "
                          "of launch)")
-    ap.add_argument("--sizes", default="", help="with --arch vozinex, nilatar or medodra: which of s,m,l (default: all)")
+    ap.add_argument("--sizes", default="", help="with --arch vozinex, nilatar, medodra or luzerax: which of s,m,l (default: all)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="prompt length of --prefill-only (the full run always measures 2048 tokens)")
     a = ap.parse_args(argv)
@@ -746,6 +814,8 @@ def main(argv=None) -> int:
         return bench_nilatar(a)
     if a.arch == "medodra" and a.gpus == 1:
         return bench_medodra(a)
+    if a.arch == "luzerax" and a.gpus == 1:
+        return bench_luzerax(a)
     if a.gpus != 1:
         print("kindi_b200 is a one-GPU library: bench.py measures N=1 only (asked for --gpus %d)" % a.gpus)
         return 2
