@@ -8,8 +8,9 @@
 //   - rotated: the pairs (i, i + rot/2) turn by pos * inv_freq[i] (rot = 0: no rotation),
 // the norm before the rotation (mode 1) or after it (mode 2; mode 0: no norm). Query heads are then multiplied by a
 // temperature that grows with the position, 1 + coef * ln(floor((pos + 1) / every) + 1) (coef = 0: none). Queries go
-// to qout, keys and values to the row's place in its cache page. A warp owns a head from the sums to the
-// temperature, so nothing but the row's load and its store meets a block barrier. All of it is 32-bit (EXACT: angles,
+// to qout, keys and values to the row's place in its cache page. A warp owns a head from its load to its store and a
+// block is a row's next eight heads, so a decode step of few rows still fills the SMs and nothing but the angles
+// meets a block barrier. All of it is 32-bit (EXACT: angles,
 // cosines and sines in 64-bit from a 64-bit frequency table, for the true 32-bit path); each value is rounded to the
 // run dtype once, when it is written.
 //
@@ -32,6 +33,7 @@
 
 #define HW_THREADS 256
 
+#define HW_HEADS (HW_THREADS / 32)      // heads of a block: one per warp
 template <typename TIN, typename T, bool EXACT>
 __global__ void __launch_bounds__(HW_THREADS) k_headnorm_rope_store(const TIN* KB_STEP_DATA in, int n_planes,
         size_t plane_stride, int ld_in, T* qout, int ldq, const float* __restrict__ gq, const float* __restrict__ gk,
@@ -45,9 +47,9 @@ __global__ void __launch_bounds__(HW_THREADS) k_headnorm_rope_store(const TIN* K
     const int p = pos[t];
     if (p < 0) return;                               // a padding row of a recorded step
     const int half = rot / 2;
-    const int n_q = nh * hd, n_k = nkv * hd, n_all = n_q + 2 * n_k;
-    float* row = sm;                                 // [n_all]
-    float2* cs = (float2*)(sm + ((n_all + 1) & ~1)); // [half]: cosine and sine of the row's angles
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* hr = sm + (size_t)warp * hd;              // this warp's head
+    float2* cs = (float2*)(sm + (((size_t)HW_HEADS * hd + 1) & ~(size_t)1));    // [half]: cosine and sine of the row's angles
     int page = -1;
     if (nkv_store > 0) {
         const int s = slot[seq[t]];
@@ -66,18 +68,19 @@ __global__ void __launch_bounds__(HW_THREADS) k_headnorm_rope_store(const TIN* K
     }
     float temp = 1.0f;
     if (t_coef != 0.0f) temp = 1.0f + t_coef * logf((float)((p + 1) / t_every + 1));
+    __syncthreads();                                 // (the angles)
     kb_pdl_wait();
-    if (nkv_store > 0 && page < 0 && threadIdx.x == 0) atomicOr(status, KB_ST_BAD_PAGE);
-    const TIN* src = in + (size_t)t * ld_in;
-    for (int i = threadIdx.x; i < n_all; i += HW_THREADS) {
+    if (nkv_store > 0 && page < 0 && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, KB_ST_BAD_PAGE);
+    const int h = blockIdx.y * HW_HEADS + warp;      // among [q heads | k heads | v heads]
+    if (h >= nh + 2 * nkv) return;
+    const TIN* src = in + (size_t)t * ld_in + (size_t)h * hd;
+    for (int i = lane; i < hd; i += 32) {
         float v = kb_to_f<TIN>(src[i]);
         for (int s = 1; s < n_planes; s++) v += kb_to_f<TIN>(src[(size_t)s * plane_stride + i]);
-        row[i] = v;
+        hr[i] = v;
     }
-    __syncthreads();                                 // (the row and the angles)
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int h = warp; h < nh + nkv; h += HW_THREADS / 32) {
-        float* hr = row + (size_t)h * hd;
+    __syncwarp();
+    if (h < nh + nkv) {
         const float* gain = h < nh ? gq : gk;
         for (int step = 0; step < 2; step++) {
             const bool do_norm = (step == 0 && norm_mode == 1) || (step == 1 && norm_mode == 2);
@@ -103,20 +106,14 @@ __global__ void __launch_bounds__(HW_THREADS) k_headnorm_rope_store(const TIN* K
                 __syncwarp();
             }
         }
-        if (h < nh && t_coef != 0.0f) {
-            for (int i = lane; i < hd; i += 32) hr[i] = __fmul_rn(hr[i], temp);
-        }
     }
-    __syncthreads();
-    for (int e = threadIdx.x; e < n_q; e += HW_THREADS)
-        qout[(size_t)t * ldq + e] = kb_from_f<T>(row[e]);
-    if (page >= 0) {
-        for (int e = threadIdx.x; e < 2 * nkv_store * hd; e += HW_THREADS) {
-            const int h = e / hd, i = e % hd;
-            const int kv = h >= nkv_store ? 1 : 0, hk = h - kv * nkv_store;
-            ((T*)cv.pool)[kb_kv_offset(cv, page, kv, hk, p % KB_PAGE) + i] =
-                kb_from_f<T>(row[n_q + (size_t)kv * n_k + (size_t)hk * hd + i]);
-        }
+    if (h < nh) {
+        T* dst = qout + (size_t)t * ldq + (size_t)h * hd;
+        for (int i = lane; i < hd; i += 32) dst[i] = kb_from_f<T>(t_coef != 0.0f ? __fmul_rn(hr[i], temp) : hr[i]);
+    } else if (page >= 0) {
+        const int kv = h >= nh + nkv ? 1 : 0, hk = h - nh - kv * nkv;
+        T* dst = (T*)cv.pool + kb_kv_offset(cv, page, kv, hk, p % KB_PAGE);
+        for (int i = lane; i < hd; i += 32) dst[i] = kb_from_f<T>(hr[i]);
     }
 }
 
@@ -131,16 +128,17 @@ extern "C" int kb_headnorm_rope_store(const void* in, int in_dtype, int n_planes
         (t_coef != 0.0f && t_every < 1) || (nkv_store != 0 && nkv_store != nkv))
         return (int)cudaErrorInvalidValue;
     KbCacheView cv{pool, table, table_stride, n_pages, nkv, hd};
-    const int n_all = (nh + 2 * nkv) * hd;
-    const size_t smem = (size_t)((n_all + 1) & ~1) * sizeof(float) + (size_t)(rot / 2) * sizeof(float2);
-    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    const int n_heads = nh + 2 * nkv;
+    const size_t smem = ((size_t)(HW_HEADS * hd + 1) & ~(size_t)1) * sizeof(float) + (size_t)(rot / 2) * sizeof(float2);
+    if (smem > 200 * 1024 || n_heads > 65535 * HW_HEADS) return (int)cudaErrorInvalidValue;
+    const dim3 grid(T, (n_heads + HW_HEADS - 1) / HW_HEADS);
     cudaError_t e = cudaSuccess;
 #define KB_HW(TIN, T_, EX)                                                                                         \
     do {                                                                                                           \
         if (smem > 48 * 1024)                                                                                      \
             cudaFuncSetAttribute(k_headnorm_rope_store<TIN, T_, EX>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                                  (int)smem);                                                                       \
-        e = kb_launch(k_headnorm_rope_store<TIN, T_, EX>, T, HW_THREADS, smem, st, (const TIN*)in, n_planes,       \
+        e = kb_launch(k_headnorm_rope_store<TIN, T_, EX>, grid, HW_THREADS, smem, st, (const TIN*)in, n_planes,    \
                       (size_t)plane_stride, ld_in, (T_*)qout, ldq, gq, gk, eps, dim_true, norm_mode, inv_freq,     \
                       inv_freq64, rot, t_coef, t_every, pos, seq, slot, nh, nkv, nkv_store, hd, cv, status);       \
     } while (0)
@@ -188,13 +186,57 @@ __global__ void __launch_bounds__(HW_THREADS) k_diff_combine(const T* KB_STEP_DA
     }
 }
 
+// the same with VEC neighbouring elements a lane (bf16, hd = 32 VEC): one load of each map, one store
+template <int VEC>
+__global__ void __launch_bounds__(HW_THREADS) k_diff_combine_vec(const bf16* KB_STEP_DATA a, int lda, bf16* out,
+        int ldo, int n_rows, int H, int r, int vd, float lambda, float eps, float mult) {
+    constexpr int hd = 32 * VEC;
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (HW_THREADS / 32) + (threadIdx.x >> 5);
+    if (item >= (long long)n_rows * H) return;
+    const int t = (int)(item / H), h = (int)(item % H);
+    const int g = h / r, i = h % r;
+    const bf16* a1 = a + (size_t)t * lda + (size_t)((g * 2 + 0) * r + i) * hd + lane * VEC;
+    const bf16* a2 = a + (size_t)t * lda + (size_t)((g * 2 + 1) * r + i) * hd + lane * VEC;
+    bf16 x1[VEC], x2[VEC], y[VEC];
+    if (VEC == 4) {
+        *(uint2*)x1 = *(const uint2*)a1;
+        *(uint2*)x2 = *(const uint2*)a2;
+    } else {
+        *(uint32_t*)x1 = *(const uint32_t*)a1;
+        *(uint32_t*)x2 = *(const uint32_t*)a2;
+    }
+    float v[VEC], ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < VEC; c++) {
+        v[c] = lane * VEC + c < vd ? __fsub_rn(__bfloat162float(x1[c]), __fmul_rn(lambda, __bfloat162float(x2[c]))) : 0.0f;
+        ss = fmaf(v[c], v[c], ss);
+    }
+    ss = kb_warp_sum(ss);
+    const float f = 1.0f / sqrtf(ss / (float)vd + eps);
+#pragma unroll
+    for (int c = 0; c < VEC; c++) y[c] = __float2bfloat16_rn(__fmul_rn(__fmul_rn(v[c], f), mult));
+    bf16* o = out + (size_t)t * ldo + (size_t)h * hd + lane * VEC;
+    if (VEC == 4) *(uint2*)o = *(const uint2*)y;
+    else *(uint32_t*)o = *(const uint32_t*)y;
+}
+
 extern "C" int kb_diff_combine(const void* a, int dtype, int lda, void* out, int ldo, int T, int H, int r, int hd,
                                int vd, float lambda, float eps, float mult, cudaStream_t st) {
     if (T <= 0 || H <= 0) return 0;
     if (r < 1 || H % r || vd < 1 || vd > hd) return (int)cudaErrorInvalidValue;
     const long long items = (long long)T * H;
     const int grid = (int)((items + HW_THREADS / 32 - 1) / (HW_THREADS / 32));
-    if (dtype == KB_F32)
+    const bool al = lda % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)a % 8) == 0 && ((uintptr_t)out % 8) == 0;
+    if (dtype == KB_BF16 && al && hd == 128)
+        kb_launch(k_diff_combine_vec<4>, grid, HW_THREADS, 0, st, (const bf16*)a, lda, (bf16*)out, ldo, T, H, r, vd,
+                  lambda, eps, mult);
+    else if (dtype == KB_BF16 && al && hd == 64)
+        kb_launch(k_diff_combine_vec<2>, grid, HW_THREADS, 0, st, (const bf16*)a, lda, (bf16*)out, ldo, T, H, r, vd,
+                  lambda, eps, mult);
+    else if (dtype == KB_F32)
         kb_launch(k_diff_combine<float>, grid, HW_THREADS, 0, st, (const float*)a, lda, (float*)out, ldo, T, H, r, hd,
                   vd, lambda, eps, mult);
     else if (dtype == KB_BF16)
@@ -219,11 +261,46 @@ __global__ void __launch_bounds__(HW_THREADS) k_head_gate_mul(const TA* KB_STEP_
     out[t * ldo + c] = kb_from_f<TA>(kb_to_f<TA>(a[t * lda + c]) * (1.0f / (1.0f + expf(-z))));
 }
 
+// bf16 rows, eight neighbouring elements a thread (hd a multiple of 8: they share a head and its gate)
+template <typename TG>
+__global__ void __launch_bounds__(HW_THREADS) k_head_gate_mul8(const bf16* KB_STEP_DATA a, int lda,
+        const TG* KB_STEP_DATA g, int n_planes, size_t plane_stride, int ldg, bf16* out, int ldo, int N, int hd) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int c = (blockIdx.y * HW_THREADS + threadIdx.x) * 8;
+    if (c >= N) return;
+    const size_t t = blockIdx.x;
+    const TG* gp = g + t * ldg + c / hd;
+    float z = kb_to_f<TG>(gp[0]);
+    for (int s = 1; s < n_planes; s++) z += kb_to_f<TG>(gp[(size_t)s * plane_stride]);
+    const float w = __fdividef(1.0f, 1.0f + __expf(-z));
+    uint4 v = *(const uint4*)(a + t * lda + c);
+    __nv_bfloat162* v2 = (__nv_bfloat162*)&v;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 f = __bfloat1622float2(v2[j]);
+        v2[j] = __floats2bfloat162_rn(f.x * w, f.y * w);
+    }
+    *(uint4*)(out + t * ldo + c) = v;
+}
+
 extern "C" int kb_head_gate_mul(const void* a, int adtype, int lda, const void* g, int gdtype, int n_planes,
                                 long long plane_stride, int ldg, void* out, int ldo, int T, int N, int hd,
                                 cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
     if (hd < 1) return (int)cudaErrorInvalidValue;
+    if (adtype == KB_BF16 && hd % 8 == 0 && lda % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)a % 16) == 0 &&
+        ((uintptr_t)out % 16) == 0) {
+        dim3 grid8(T, (N / 8 + HW_THREADS - 1) / HW_THREADS);
+        if (gdtype == KB_BF16)
+            kb_launch(k_head_gate_mul8<bf16>, grid8, HW_THREADS, 0, st, (const bf16*)a, lda, (const bf16*)g, n_planes,
+                      (size_t)plane_stride, ldg, (bf16*)out, ldo, N, hd);
+        else if (gdtype == KB_F32)
+            kb_launch(k_head_gate_mul8<float>, grid8, HW_THREADS, 0, st, (const bf16*)a, lda, (const float*)g,
+                      n_planes, (size_t)plane_stride, ldg, (bf16*)out, ldo, N, hd);
+        else return (int)cudaErrorInvalidValue;
+        KB_LAUNCH_RET();
+    }
     dim3 grid(T, (N + HW_THREADS - 1) / HW_THREADS);
 #define KB_HG(TA, TG)                                                                                              \
     kb_launch(k_head_gate_mul<TA, TG>, grid, HW_THREADS, 0, st, (const TA*)a, lda, (const TG*)g, n_planes,         \
@@ -380,6 +457,34 @@ __global__ void __launch_bounds__(256) k_glu_clamp(const TIN* KB_STEP_DATA gu, i
     out[t * ldo + c] = kb_from_f<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
 }
 
+// bf16 rows in, bf16 out, eight columns a thread with 16-byte accesses; exp and the division by the fast intrinsics
+// (their error is far below one bf16 rounding)
+__global__ void __launch_bounds__(256) k_glu_clamp8(const bf16* KB_STEP_DATA gu, int ldg, bf16* out, int ldo, int F,
+                                                    int group, float limit, float alpha) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
+    if (c >= F) return;
+    const size_t t = blockIdx.y;
+    const bf16* g0 = gu + t * ldg + (size_t)(c / group) * 2 * group + c % group;
+    const uint4 gv = *(const uint4*)g0, uv = *(const uint4*)(g0 + group);
+    const __nv_bfloat162* g2 = (const __nv_bfloat162*)&gv;
+    const __nv_bfloat162* u2 = (const __nv_bfloat162*)&uv;
+    uint4 ov;
+    __nv_bfloat162* o2 = (__nv_bfloat162*)&ov;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+        g.x = fminf(g.x, limit);
+        g.y = fminf(g.y, limit);
+        u.x = fminf(fmaxf(u.x, -limit), limit) + 1.0f;
+        u.y = fminf(fmaxf(u.y, -limit), limit) + 1.0f;
+        o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-alpha * g.x)) * u.x,
+                                      __fdividef(g.y, 1.0f + __expf(-alpha * g.y)) * u.y);
+    }
+    *(uint4*)(out + t * ldo + c) = ov;
+}
+
 extern "C" int kb_glu_clamp(const void* gu, int in_dtype, int n_planes, long long plane_stride, int ldg, void* out,
                             int dtype, int ldo, int R, int F, int group, float limit, float alpha, cudaStream_t st) {
     if (R <= 0 || F <= 0) return 0;
@@ -390,7 +495,11 @@ extern "C" int kb_glu_clamp(const void* gu, int in_dtype, int n_planes, long lon
         const size_t in_el = in_dtype == KB_F32 ? 4 : 2, out_el = dtype == KB_F32 ? 4 : 2;
         const void* gi = (const char*)gu + (size_t)r0 * ldg * in_el;
         void* oi = (char*)out + (size_t)r0 * ldo * out_el;
-        if (in_dtype == KB_F32 && dtype == KB_F32)
+        if (in_dtype == KB_BF16 && dtype == KB_BF16 && n_planes == 1 && F % 8 == 0 && group % 8 == 0 && ldg % 8 == 0 &&
+            ldo % 8 == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+            dim3 g8((F / 8 + 255) / 256, n);
+            kb_launch(k_glu_clamp8, g8, 256, 0, st, (const bf16*)gi, ldg, (bf16*)oi, ldo, F, group, limit, alpha);
+        } else if (in_dtype == KB_F32 && dtype == KB_F32)
             kb_launch(k_glu_clamp<float, float>, grid, 256, 0, st, (const float*)gi, n_planes, (size_t)plane_stride,
                       ldg, (float*)oi, ldo, F, group, limit, alpha);
         else if (in_dtype == KB_F32 && dtype == KB_BF16)
