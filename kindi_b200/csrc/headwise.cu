@@ -117,6 +117,128 @@ __global__ void __launch_bounds__(HW_THREADS) k_headnorm_rope_store(const TIN* K
     }
 }
 
+// The same for heads of 32 * NE elements that are rotated as a whole or not at all (rot == hd or 0), with 16-byte
+// aligned rows: a lane holds NE neighbouring elements of the head in registers (one load), its partner in the
+// rotation is lane ^ 16, the head's sum of squares is one warp reduction, and nothing goes through shared memory.
+// A warp walks the heads h, h + 8 gridDim.y, ... of its row with the row's cosines and sines in registers.
+template <int N> struct HwVec;
+template <> struct HwVec<2> { typedef uint32_t b; typedef float2 f; };
+template <> struct HwVec<4> { typedef uint2 b; typedef float4 f; };
+template <int NE> __device__ __forceinline__ void hw_load(const float* p, float* o) {
+    const typename HwVec<NE>::f v = *(const typename HwVec<NE>::f*)p;
+#pragma unroll
+    for (int e = 0; e < NE; e++) o[e] = ((const float*)&v)[e];
+}
+template <int NE> __device__ __forceinline__ void hw_load(const bf16* p, float* o) {
+    const typename HwVec<NE>::b v = *(const typename HwVec<NE>::b*)p;
+#pragma unroll
+    for (int e = 0; e < NE; e++) o[e] = __bfloat162float(((const bf16*)&v)[e]);
+}
+template <int NE> __device__ __forceinline__ void hw_store(float* p, const float* o) {
+    typename HwVec<NE>::f v;
+#pragma unroll
+    for (int e = 0; e < NE; e++) ((float*)&v)[e] = o[e];
+    *(typename HwVec<NE>::f*)p = v;
+}
+template <int NE> __device__ __forceinline__ void hw_store(bf16* p, const float* o) {
+    typename HwVec<NE>::b v;
+#pragma unroll
+    for (int e = 0; e < NE; e++) ((bf16*)&v)[e] = __float2bfloat16_rn(o[e]);
+    *(typename HwVec<NE>::b*)p = v;
+}
+
+template <typename TIN, typename T, int NE, bool EXACT>
+__global__ void __launch_bounds__(HW_THREADS) k_headnorm_rope_store_reg(const TIN* KB_STEP_DATA in, int n_planes,
+        size_t plane_stride, int ld_in, T* qout, int ldq, const float* __restrict__ gq, const float* __restrict__ gk,
+        float eps, int dim_true, int norm_mode, const float* __restrict__ inv_freq,
+        const double* __restrict__ inv_freq64, int rot, float t_coef, int t_every, const int* __restrict__ pos,
+        const int* __restrict__ seq, const int* __restrict__ slot, int nh, int nkv, int nkv_store, KbCacheView cv,
+        int* status) {
+    constexpr int hd = 32 * NE;
+    kb_pdl_launch();
+    const int t = blockIdx.x;
+    const int p = pos[t];
+    if (p < 0) return;                               // a padding row of a recorded step
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e0 = lane * NE;                        // this lane's elements of a head
+    int page = -1;
+    if (nkv_store > 0) {
+        const int s = slot[seq[t]];
+        page = cv.table[(size_t)s * cv.table_stride + p / KB_PAGE];
+        if (page < 0 || page >= cv.n_pages) page = -1;
+    }
+    float c[NE], sn[NE], wq[NE], wk[NE];
+#pragma unroll
+    for (int e = 0; e < NE; e++) {
+        c[e] = 1.0f;
+        sn[e] = 0.0f;
+        if (rot > 0) {
+            const int i = (lane & 15) * NE + e;      // the pair's index: elements i and i + hd / 2
+            if (EXACT) {
+                double s_, c_;
+                sincos((double)p * inv_freq64[i], &s_, &c_);
+                c[e] = (float)c_;
+                sn[e] = (float)s_;
+            } else {
+                const float ang = __fmul_rn((float)p, inv_freq[i]);
+                c[e] = cosf(ang);
+                sn[e] = sinf(ang);
+            }
+            if (lane < 16) sn[e] = -sn[e];           // element i: a c - b s; element i + hd / 2: b c + a s
+        }
+        wq[e] = gq ? gq[e0 + e] : 1.0f;
+        wk[e] = gk ? gk[e0 + e] : 1.0f;
+    }
+    float temp = 1.0f;
+    if (t_coef != 0.0f) temp = 1.0f + t_coef * logf((float)((p + 1) / t_every + 1));
+    kb_pdl_wait();
+    if (nkv_store > 0 && page < 0 && threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, KB_ST_BAD_PAGE);
+    for (int h = blockIdx.y * HW_HEADS + warp; h < nh + 2 * nkv; h += gridDim.y * HW_HEADS) {
+        const TIN* src = in + (size_t)t * ld_in + (size_t)h * hd + e0;
+        float v[NE];
+        hw_load<NE>(src, v);
+        for (int s = 1; s < n_planes; s++) {
+            float u[NE];
+            hw_load<NE>(src + (size_t)s * plane_stride, u);
+#pragma unroll
+            for (int e = 0; e < NE; e++) v[e] += u[e];
+        }
+        if (h < nh + nkv) {
+#pragma unroll
+            for (int step = 0; step < 2; step++) {
+                const bool do_norm = (step == 0 && norm_mode == 1) || (step == 1 && norm_mode == 2);
+                const bool do_rot = (step == 0 && norm_mode == 2) || (step == 1 && norm_mode != 2);
+                if (do_norm) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < NE; e++) ss = fmaf(v[e], v[e], ss);
+                    ss = kb_warp_sum(ss);
+                    const float f = 1.0f / sqrtf(ss / (float)dim_true + eps);
+#pragma unroll
+                    for (int e = 0; e < NE; e++) v[e] = __fmul_rn(__fmul_rn(v[e], f), h < nh ? wq[e] : wk[e]);
+                }
+                if (do_rot && rot > 0) {
+#pragma unroll
+                    for (int e = 0; e < NE; e++) {
+                        const float o = __shfl_xor_sync(0xffffffffu, v[e], 16);
+                        v[e] = __fadd_rn(__fmul_rn(v[e], c[e]), __fmul_rn(o, sn[e]));
+                    }
+                }
+            }
+        }
+        if (h < nh) {
+            if (t_coef != 0.0f) {
+#pragma unroll
+                for (int e = 0; e < NE; e++) v[e] = __fmul_rn(v[e], temp);
+            }
+            hw_store<NE>(qout + (size_t)t * ldq + (size_t)h * hd + e0, v);
+        } else if (page >= 0) {
+            const int kv = h >= nh + nkv ? 1 : 0, hk = h - nh - kv * nkv;
+            hw_store<NE>((T*)cv.pool + kb_kv_offset(cv, page, kv, hk, p % KB_PAGE) + e0, v);
+        }
+    }
+}
+
 extern "C" int kb_headnorm_rope_store(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in,
                                       void* qout, int dtype, int ldq, const float* gq, const float* gk, float eps,
                                       int dim_true, int norm_mode, const float* inv_freq, const double* inv_freq64,
@@ -133,6 +255,32 @@ extern "C" int kb_headnorm_rope_store(const void* in, int in_dtype, int n_planes
     if (smem > 200 * 1024 || n_heads > 65535 * HW_HEADS) return (int)cudaErrorInvalidValue;
     const dim3 grid(T, (n_heads + HW_HEADS - 1) / HW_HEADS);
     cudaError_t e = cudaSuccess;
+    // heads of 64 or 128 rotated as a whole or not at all, aligned rows: the form that keeps a head in registers; a
+    // prompt-sized step gives a block all heads of its row, a small step spreads a row's heads over blocks
+    const int in_el = in_dtype == KB_F32 ? 4 : 2, out_el = dtype == KB_F32 ? 4 : 2;
+    const int ne = hd / 32;
+    if ((hd == 64 || hd == 128) && (rot == 0 || rot == hd) && ld_in % ne == 0 && ldq % ne == 0 && plane_stride % ne == 0 &&
+        ((uintptr_t)in % (ne * in_el)) == 0 && ((uintptr_t)qout % (ne * out_el)) == 0 &&
+        ((uintptr_t)pool % (ne * out_el)) == 0) {
+        const int want = (n_heads + HW_HEADS - 1) / HW_HEADS;
+        const int gy = T >= 1024 ? 1 : T >= 256 ? (want < 2 ? want : 2) : want;
+        const dim3 gridr(T, gy);
+#define KB_HWR(TIN, T_, NE, EX)                                                                                    \
+        e = kb_launch(k_headnorm_rope_store_reg<TIN, T_, NE, EX>, gridr, HW_THREADS, 0, st, (const TIN*)in, n_planes, \
+                      (size_t)plane_stride, ld_in, (T_*)qout, ldq, gq, gk, eps, dim_true, norm_mode, inv_freq,     \
+                      inv_freq64, rot, t_coef, t_every, pos, seq, slot, nh, nkv, nkv_store, cv, status)
+#define KB_HWR2(TIN, T_, EX) do { if (ne == 4) KB_HWR(TIN, T_, 4, EX); else KB_HWR(TIN, T_, 2, EX); } while (0)
+        if (in_dtype == KB_F32 && dtype == KB_F32) {
+            if (rot > 0 && inv_freq64 == nullptr) return (int)cudaErrorInvalidValue;
+            KB_HWR2(float, float, true);
+        } else if (rot > 0 && inv_freq == nullptr) return (int)cudaErrorInvalidValue;
+        else if (in_dtype == KB_F32 && dtype == KB_BF16) KB_HWR2(float, bf16, false);
+        else if (in_dtype == KB_BF16 && dtype == KB_BF16) KB_HWR2(bf16, bf16, false);
+        else return (int)cudaErrorInvalidValue;
+#undef KB_HWR2
+#undef KB_HWR
+        return (int)e;
+    }
 #define KB_HW(TIN, T_, EX)                                                                                         \
     do {                                                                                                           \
         if (smem > 48 * 1024)                                                                                      \

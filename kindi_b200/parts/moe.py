@@ -96,8 +96,8 @@ class MixtureOfExperts(FeedForward):
     def __init__(self, spec, width, weights: WeightView, *, dtype, device):
         super().__init__(spec, width, weights, dtype=dtype, device=device)
         self.E, self.top, self.f = self._sizes(spec)
-        if not (1 <= self.top <= self.E):
-            raise ValueError("top_k %d must lie between 1 and n_experts %d" % (self.top, self.E))
+        if not (1 <= self.top <= self.E + int(spec.get("identity") or 0)):
+            raise ValueError("top_k %d must lie between 1 and the %d experts" % (self.top, self.E + int(spec.get("identity") or 0)))
         self.act = str(spec.get("activation", "relu2"))
         if self.act not in K.ACT and not (self.act == "glu_clamp" and spec.get("gated")):
             raise ValueError("unknown activation %r; known: %s, and glu_clamp for gated experts"
