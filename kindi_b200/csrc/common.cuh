@@ -81,6 +81,30 @@ __device__ __forceinline__ float kb_gate_act_fast(float g, int act) {
     return __fdividef(g, 1.0f + __expf(e));
 }
 
+// the gated unit a product finishes in its epilogue: which activation, and for the clamped unit its two constants.
+// KB_ACT_GLU_CLAMP: g' sigmoid(alpha g') (u' + 1) with g' = min(g, lim), u' = clamp(u, -lim, lim)
+#define KB_ACT_GLU_CLAMP 4
+struct KbGate {
+    int act;
+    float lim, alpha;
+};
+__device__ __forceinline__ float kb_glu_fast(float g, float u, const KbGate& k) {
+    if (k.act == KB_ACT_GLU_CLAMP) {
+        g = fminf(g, k.lim);
+        u = fminf(fmaxf(u, -k.lim), k.lim) + 1.0f;
+        return __fdividef(g, 1.0f + __expf(-k.alpha * g)) * u;
+    }
+    return kb_gate_act_fast(g, k.act) * u;
+}
+// (an entry point's activation code: 0, 1 and KB_ACT_SILU all mean silu)
+static inline KbGate kb_gate_of(int act, float lim, float alpha) {
+    KbGate k;
+    k.act = act == KB_ACT_GELU_TANH ? KB_ACT_GELU_TANH : act == KB_ACT_GLU_CLAMP ? KB_ACT_GLU_CLAMP : KB_ACT_SILU;
+    k.lim = lim;
+    k.alpha = alpha;
+    return k;
+}
+
 #define KB_LAUNCH_RET() return (int)cudaGetLastError()
 
 // Programmatic dependent launch. Every kernel of the library begins with kb_pdl_launch() (when its grid is small,

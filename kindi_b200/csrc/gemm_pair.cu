@@ -95,7 +95,7 @@ __device__ __forceinline__ void gp_umma_commit(uint32_t bar) {
 template <int BN, int STAGES, typename TC>
 __global__ void __launch_bounds__(GP_THREADS) k_gemm_pair(const __grid_constant__ CUtensorMap mapA,
         const __grid_constant__ CUtensorMap mapW, TC* __restrict__ C, int M, int N, int K, int ldc, int* status,
-        int swiglu_ld, float* part, int* flags, int gate_act) {      // (part, flags: shared with other CTAs of this launch: no __restrict__)
+        int swiglu_ld, float* part, int* flags, KbGate gate_act) {      // (part, flags: shared with other CTAs of this launch: no __restrict__)
     using S = GpSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -301,8 +301,8 @@ __global__ void __launch_bounds__(GP_THREADS) k_gemm_pair(const __grid_constant_
                         for (int c = 0; c < 8; c++) {
                             const float g0 = __uint_as_float(gu[2 * c]), g1 = __uint_as_float(gu[2 * c + 1]);
                             __nv_bfloat162 v = __floats2bfloat162_rn(
-                                kb_gate_act_fast(g0, gate_act) * __uint_as_float(gu[16 + 2 * c]),
-                                kb_gate_act_fast(g1, gate_act) * __uint_as_float(gu[16 + 2 * c + 1]));
+                                kb_glu_fast(g0, __uint_as_float(gu[16 + 2 * c]), gate_act),
+                                kb_glu_fast(g1, __uint_as_float(gu[16 + 2 * c + 1]), gate_act));
                             h[c] = *(uint32_t*)&v;
                         }
                         bf16* dst = orow + ((q0 + c0) >> 1);
@@ -399,7 +399,7 @@ static int gp_sm_count() {
 
 template <int BN, int STAGES, typename TC>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc, int* status,
-                       cudaStream_t st, int swiglu_ld, float* part, int* flags, int gate_act) {
+                       cudaStream_t st, int swiglu_ld, float* part, int* flags, KbGate gate_act) {
     using S = GpSmem<BN, STAGES>;
     auto kern = k_gemm_pair<BN, STAGES, TC>;
     static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
@@ -435,13 +435,14 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, in
 // ceil(M / 256) * ceil(N / bn), 16-byte aligned) and flags (8 ints a tile, zero before the first call; the kernel
 // lowers what it raised) are the scratch of tiles shared by two pairs; without them the work is cut tile by tile.
 extern "C" int kb_gemm_pair(const void* A, const void* W, void* C, int cdtype, int M, int N, int K, int lda, int ldw,
-                            int ldc, int bn, int* status, cudaStream_t st, int swiglu, float* part, int* flags) {
+                            int ldc, int bn, int* status, cudaStream_t st, int swiglu, float* part, int* flags,
+                            float act_lim = 0.0f, float act_alpha = 0.0f) {
     if (swiglu && ((N % 32) || cdtype != KB_BF16 || (ldc % 8) || ((uintptr_t)C & 15))) return (int)cudaErrorInvalidValue;
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if ((K % 8) || (lda % 8) || (ldw % 8)) return (int)cudaErrorInvalidValue;
     if (cdtype != KB_F32 && cdtype != KB_BF16) return (int)cudaErrorInvalidValue;
     const int swiglu_ld = swiglu ? ldc : 0;
-    const int gate_act = swiglu == KB_ACT_GELU_TANH ? KB_ACT_GELU_TANH : KB_ACT_SILU;   // (1 and KB_ACT_SILU: silu)
+    const KbGate gate_act = kb_gate_of(swiglu, act_lim, act_alpha);
     CUtensorMap ma, mw;
     int rc;
     if ((rc = kb_make_map_bf16(&ma, A, M, K, lda, GP_BM))) return rc;

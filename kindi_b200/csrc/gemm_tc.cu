@@ -42,7 +42,7 @@ struct TcSmem {
 template <int BN, int STAGES, bool SWAP, typename TC, int MT = 1>
 __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ CUtensorMap mapP,
         const __grid_constant__ CUtensorMap mapQ, TC* __restrict__ C, int rowsP, int rowsQ, int K, int ldc,
-        long long split_stride, int kb_per_split, int n_splits, int* status, int swiglu_ld, int gate_act) {
+        long long split_stride, int kb_per_split, int n_splits, int* status, int swiglu_ld, KbGate gate_act) {
     using S = TcSmem<BN, STAGES, MT, SWAP>;
     static_assert(MT == 1 || (!SWAP && 2 * BN <= 512), "two row tiles: prefill form, both accumulators in tensor memory");
     extern __shared__ uint8_t smem_raw[];
@@ -198,8 +198,8 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                         for (int c = 0; c < 8; c++) {
                             const float g0 = __uint_as_float(gu[2 * c]), g1 = __uint_as_float(gu[2 * c + 1]);
                             __nv_bfloat162 v = __floats2bfloat162_rn(
-                                kb_gate_act_fast(g0, gate_act) * __uint_as_float(gu[16 + 2 * c]),
-                                kb_gate_act_fast(g1, gate_act) * __uint_as_float(gu[16 + 2 * c + 1]));
+                                kb_glu_fast(g0, __uint_as_float(gu[16 + 2 * c]), gate_act),
+                                kb_glu_fast(g1, __uint_as_float(gu[16 + 2 * c + 1]), gate_act));
                             h[c] = *(uint32_t*)&v;
                         }
                         bf16* dst = orow + ((q0 + c0) >> 1);
@@ -308,7 +308,7 @@ static int kb_sm_count() {
 
 template <int BN, int STAGES, bool SWAP, typename TC, int MT = 1>
 static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int rowsP, int rowsQ, int K, int ldc,
-                     int splits, long long split_stride, int* status, cudaStream_t st, int swiglu_ld, int gate_act) {
+                     int splits, long long split_stride, int* status, cudaStream_t st, int swiglu_ld, KbGate gate_act) {
     using S = TcSmem<BN, STAGES, MT, SWAP>;
     auto kern = k_gemm_tc<BN, STAGES, SWAP, TC, MT>;
     static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
@@ -342,7 +342,7 @@ static int launch_tc(const CUtensorMap& mp, const CUtensorMap& mq, void* C, int 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS) k_gemm_sk_swiglu(const __grid_constant__ CUtensorMap mapP,
         const __grid_constant__ CUtensorMap mapQ, bf16* __restrict__ H, int rowsP, int M, int K, int F, int ldh,
-        float* part, int* flags, int* status, int gate_act) {      // (part, flags: shared with other CTAs of this launch: no __restrict__)
+        float* part, int* flags, int* status, KbGate gate_act) {      // (part, flags: shared with other CTAs of this launch: no __restrict__)
     using S = TcSmem<BN, STAGES, 1, true>;
     extern __shared__ uint8_t smem_raw[];
     kb_pdl_launch_now();
@@ -505,7 +505,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_sk_swiglu(const __grid_cons
                     if (shared_owner) v += other[c0 + c];
                     const float u = __shfl_xor_sync(0xffffffffu, v, 16);          // lanes 0..15: gate; their partners: up
                     if (lane < 16 && c0 + c < M && feat < F)
-                        H[(size_t)(c0 + c) * ldh + feat] = __float2bfloat16_rn(kb_gate_act_fast(v, gate_act) * u);
+                        H[(size_t)(c0 + c) * ldh + feat] = __float2bfloat16_rn(kb_glu_fast(v, u, gate_act));
                 }
             }
             if (helper) {
@@ -528,7 +528,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_sk_swiglu(const __grid_cons
 
 template <int BN, int STAGES>
 static int launch_sk_swiglu(const CUtensorMap& mp, const CUtensorMap& mq, void* H, int rowsP, int M, int K, int F,
-                            int ldh, float* part, int* flags, int* status, cudaStream_t st, int gate_act) {
+                            int ldh, float* part, int* flags, int* status, cudaStream_t st, KbGate gate_act) {
     using S = TcSmem<BN, STAGES, 1, true>;
     auto kern = k_gemm_sk_swiglu<BN, STAGES>;
     static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
@@ -547,10 +547,11 @@ static int launch_sk_swiglu(const CUtensorMap& mp, const CUtensorMap& mq, void* 
 // ([ceil(2F / 128)] ints, zero before the first call and left zero by every call that ends without an error) are the
 // caller's; calls that share them must be ordered on one stream.
 extern "C" int kb_gemm_swiglu_decode(const void* A, const void* W, void* H, int M, int F, int K, int lda, int ldw, int ldh,
-                                     int bn, float* part, int* flags, int* status, cudaStream_t st, int act) {
-    // act: the gate's activation, KB_ACT_SILU (or 0) or KB_ACT_GELU_TANH
+                                     int bn, float* part, int* flags, int* status, cudaStream_t st, int act,
+                                     float act_lim = 0.0f, float act_alpha = 0.0f) {
+    // act: the gate's activation, KB_ACT_SILU (or 0), KB_ACT_GELU_TANH, or KB_ACT_GLU_CLAMP with its limit and alpha
     if (M <= 0 || F <= 0 || K <= 0) return 0;
-    const int gate_act = act == KB_ACT_GELU_TANH ? KB_ACT_GELU_TANH : KB_ACT_SILU;
+    const KbGate gate_act = kb_gate_of(act, act_lim, act_alpha);
     if ((K % 8) || (lda % 8) || (ldw % 8) || (F % 16) || M > bn || !part || !flags) return (int)cudaErrorInvalidValue;
     if ((long long)((2 * (long long)F + TC_BM - 1) / TC_BM) * ((K + TC_BK - 1) / TC_BK) > 0x3fffffffLL)
         return (int)cudaErrorInvalidValue;
@@ -582,12 +583,12 @@ extern "C" int kb_gemm_tc_splits(int K, int wanted) {
 // the bf16 [M][N / 2] result silu(gate) * up with row stride ldc.
 extern "C" int kb_gemm_tc(const void* A, const void* W, void* C, int cdtype, int M, int N, int K, int lda, int ldw,
                           int ldc, int swap, int bn, int splits, long long split_stride, int* status,
-                          cudaStream_t st, int swiglu = 0, int mt = 1) {
+                          cudaStream_t st, int swiglu = 0, int mt = 1, float act_lim = 0.0f, float act_alpha = 0.0f) {
     if (mt != 1 && (mt != 2 || swap || splits != 1)) return (int)cudaErrorInvalidValue;
     if (swiglu && (swap || (N % 32) || cdtype != KB_BF16 || splits != 1 || (ldc % 8) || ((uintptr_t)C & 15)))
         return (int)cudaErrorInvalidValue;
     const int swiglu_ld = swiglu ? ldc : 0;
-    const int gate_act = swiglu == KB_ACT_GELU_TANH ? KB_ACT_GELU_TANH : KB_ACT_SILU;   // (1 and KB_ACT_SILU: silu)
+    const KbGate gate_act = kb_gate_of(swiglu, act_lim, act_alpha);
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if ((K % 8) || (lda % 8) || (ldw % 8)) return (int)cudaErrorInvalidValue;
     if (splits > 1 && cdtype != KB_F32) return (int)cudaErrorInvalidValue;

@@ -129,12 +129,13 @@ _PAIR_SCRATCH = {}         # device -> (partial tiles, flags): scratch of tiles 
 
 
 def _prefill_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, swiglu: bool,
-                     act: str = "silu") -> None:
+                     act: str = "silu", act_params=None) -> None:
     m, k = a.shape
     n = w.shape[0]
     kind, bn, variant = _prefill_tile(m, n, k, swiglu)
     if kind == "tc":
-        K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=status, swiglu=swiglu, mt=variant, act=act)
+        K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=status, swiglu=swiglu, mt=variant, act=act,
+                  act_params=act_params)
         return
     part = flags = None
     if variant:
@@ -145,7 +146,7 @@ def _prefill_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status
                     torch.zeros(8 * tiles, dtype=torch.int32, device=a.device))
             _PAIR_SCRATCH[a.device] = have
         part, flags = have
-    K.gemm_pair(a, w, out, bn=bn, status=status, swiglu=swiglu, part=part, flags=flags, act=act)
+    K.gemm_pair(a, w, out, bn=bn, status=status, swiglu=swiglu, part=part, flags=flags, act=act, act_params=act_params)
 
 
 def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
@@ -184,13 +185,13 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
 
 
 def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
-                     act: str = "silu") -> bool:
+                     act: str = "silu", act_params=None) -> bool:
     """out (bf16 [M, F]) = silu(g) * u for a prompt-sized step, finished inside the product's epilogue; w_grouped
     [2F, K] holds 16 gate rows then the 16 up rows of the same outputs, group after group. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
     if _swiglu_in_decode_form(a) or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
         return False
-    _prefill_product(a, w_grouped, out, status, True, act)
+    _prefill_product(a, w_grouped, out, status, True, act, act_params)
     return True
 
 
@@ -213,7 +214,7 @@ def reset_scratch() -> None:
 
 
 def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
-                       act: str = "silu") -> bool:
+                       act: str = "silu", act_params=None) -> bool:
     """out (bf16 [M, F]) = silu(g) * u for a decode-sized step, finished inside the product (no split-K planes, no
     SwiGLU kernel); w_grouped [2F, K] as for gemm_swiglu_rows. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
@@ -227,7 +228,7 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
         _SK_SCRATCH[key] = (torch.empty(tiles * bn * 128, dtype=torch.float32, device=a.device),
                             torch.zeros(tiles, dtype=torch.int32, device=a.device))
     part, flags = _SK_SCRATCH[key]
-    K.gemm_swiglu_decode(a, w_grouped, out, bn, part, flags, status, act)
+    K.gemm_swiglu_decode(a, w_grouped, out, bn, part, flags, status, act, act_params)
     return True
 
 

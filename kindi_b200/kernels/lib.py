@@ -103,13 +103,13 @@ _SIGS = {
                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int],
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                   c_longlong, c_void_p, c_void_p, c_int, c_int],
+                   c_longlong, c_void_p, c_void_p, c_int, c_int, c_float, c_float],
     "kb_gemm_tc_splits": [c_int, c_int],
     "kb_rope_table_min_rows": [],
     "kb_gemm_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                     c_void_p, c_int, c_void_p, c_void_p],
+                     c_void_p, c_int, c_void_p, c_void_p, c_float, c_float],
     "kb_gemm_swiglu_decode": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                              c_void_p, c_void_p, c_void_p, c_int],
+                              c_void_p, c_void_p, c_void_p, c_int, c_float, c_float],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                     c_int, c_void_p],
@@ -406,7 +406,15 @@ def norm_rope_store(qkv: torch.Tensor, qout: torch.Tensor, wq: Optional[torch.Te
 
 
 ACT = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}
-GATE_ACT = {"silu": ACT["silu"], "gelu_tanh": ACT["gelu_tanh"]}      # what a gated feed-forward's gate may pass through
+# what a gated feed-forward's gate may pass through inside a product's epilogue; "glu_clamp" (with ``act_params`` =
+# (limit, alpha)): g' sigmoid(alpha g') (u' + 1), gate clamped from above, up from both sides
+GATE_ACT = {"silu": ACT["silu"], "gelu_tanh": ACT["gelu_tanh"], "glu_clamp": 4}
+
+
+def _gate_params(act: str, act_params):
+    if act == "glu_clamp":
+        return float(act_params[0]), float(act_params[1])
+    return 0.0, 0.0
 
 
 def _planes_of(g: torch.Tensor):
@@ -734,7 +742,7 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0, act: str = "silu
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, bn: int, splits: int,
-            status: torch.Tensor, swiglu: bool = False, mt: int = 1, act: str = "silu") -> None:
+            status: torch.Tensor, swiglu: bool = False, mt: int = 1, act: str = "silu", act_params=None) -> None:
     """out = a[M, K] @ w[N, K]^T on the tensor cores (bf16 in, fp32 accumulate). ``out`` is [M, N] (bf16 or fp32)
     or, with K splits, fp32 [S, M, N] where S = gemm_tc_splits(K, splits). ``swiglu`` (prefill form, bn a multiple
     of 32): w holds 16 gate rows then the 16 up rows of the same outputs, group after group, and ``out`` is the bf16
@@ -754,12 +762,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, 
         assert out.shape == (M, N) and splits == 1
         stride, ldc = 0, N
     _check(load().kb_gemm_tc(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, 1 if swap else 0,
-                             bn, splits, stride, _p(status), _stream(), GATE_ACT[act] if swiglu else 0, mt), "gemm_tc")
+                             bn, splits, stride, _p(status), _stream(), GATE_ACT[act] if swiglu else 0, mt,
+                             *_gate_params(act, act_params)), "gemm_tc")
 
 
 def gemm_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bn: int, status: torch.Tensor,
               swiglu: bool = False, part: Optional[torch.Tensor] = None, flags: Optional[torch.Tensor] = None,
-              act: str = "silu") -> None:
+              act: str = "silu", act_params=None) -> None:
     """out = a[M, K] @ w[N, K]^T by pairs of SMs (tcgen05 with cta_group::2: a pair computes 256 rows x bn columns,
     each CTA holding half of the weight tile), bf16 in, fp32 accumulate, ``out`` [M, N] bf16 or fp32; bn 64, 128, 192
     or 256. ``swiglu``: as for gemm_tc, ``out`` is the bf16 [M, N / 2] result silu(gate) * up. With ``part`` (fp32, at
@@ -781,11 +790,12 @@ def gemm_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bn: int, s
         assert part.dtype == torch.float32 and part.numel() >= tiles * 256 * bn and part.is_contiguous()
         assert flags.dtype == torch.int32 and flags.numel() >= 8 * tiles and flags.is_contiguous()
     _check(load().kb_gemm_pair(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, bn, _p(status),
-                               _stream(), GATE_ACT[act] if swiglu else 0, _p(part), _p(flags)), "gemm_pair")
+                               _stream(), GATE_ACT[act] if swiglu else 0, _p(part), _p(flags),
+                               *_gate_params(act, act_params)), "gemm_pair")
 
 
 def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, bn: int, part: torch.Tensor,
-                       flags: torch.Tensor, status: torch.Tensor, act: str = "silu") -> None:
+                       flags: torch.Tensor, status: torch.Tensor, act: str = "silu", act_params=None) -> None:
     """out (bf16 [M, F]) = silu(g) * u with [g | u] = a[M, K] @ w_grouped[2F, K]^T (16 gate rows, then the 16 up rows
     of the same outputs), for M <= bn rows, SwiGLU finished inside the product. ``part`` (float32, at least
     ceil(2F / 128) * bn * 128) and ``flags`` (int32 zeros, at least ceil(2F / 128)) are scratch that calls on one
@@ -799,8 +809,8 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
     assert F % 16 == 0 and M <= bn and part.dtype == torch.float32 and part.numel() >= tiles * bn * 128
     assert flags.dtype == torch.int32 and flags.numel() >= tiles
     _check(load().kb_gemm_swiglu_decode(_p(a), _p(w_grouped), _p(out), M, F, K, a.stride(0), w_grouped.stride(0),
-                                        out.stride(0), bn, _p(part), _p(flags), _p(status), _stream(), GATE_ACT[act]),
-           "gemm_swiglu_decode")
+                                        out.stride(0), bn, _p(part), _p(flags), _p(status), _stream(), GATE_ACT[act],
+                                        *_gate_params(act, act_params)), "gemm_swiglu_decode")
 
 
 @functools.lru_cache(maxsize=4096)

@@ -78,9 +78,13 @@ def gate_up_swiglu(ctx, y: torch.Tensor, wgu: torch.Tensor, group: int, f: int, 
 def gate_up_glu_clamp(ctx, y: torch.Tensor, wgu: torch.Tensor, group: int, f: int, out_dtype: torch.dtype,
                       limit: float, alpha: float) -> torch.Tensor:
     """``g' sigmoid(alpha g') (u' + 1)`` with ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)`` and
-    ``[g | u] = y @ wgu^T`` (``wgu`` as ``join_gate_up`` made it): the product as rows or 32-bit planes, then the
-    kernel of the clamped unit"""
+    ``[g | u] = y @ wgu^T`` (``wgu`` as ``join_gate_up`` made it): inside the product where a tensor-core kernel takes
+    the shape, else the product as rows or 32-bit planes followed by the kernel of the clamped unit"""
     h = torch.empty((y.shape[0], f), dtype=out_dtype, device=y.device)
+    if ctx.fast and group == GATE_UP_GROUP and (
+            fast.gemm_swiglu_decode(y, wgu, h, ctx.status, "glu_clamp", (limit, alpha))
+            or fast.gemm_swiglu_rows(y, wgu, h, ctx.status, "glu_clamp", (limit, alpha))):
+        return h
     gu = rows_or_planes(ctx, y, wgu, out_dtype)
     K.glu_clamp(gu, h, group, limit, alpha)
     return h

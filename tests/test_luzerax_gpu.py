@@ -214,6 +214,28 @@ def test_gate_per_head(K, dtype, planes):
     assert _rel(out.view(T, H, hd), want) < (2e-6 if dtype == "float32" else 6e-3)
 
 
+@pytest.mark.parametrize("dtype,fast", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+@pytest.mark.parametrize("M,width,F", [(1, 64, 48), (8, 256, 512), (20, 128, 96), (70, 72, 20), (300, 256, 640),
+                                       (1500, 512, 1024)])
+def test_clamped_gated_unit_alone_and_in_the_products_epilogues(K, dtype, fast, M, width, F):
+    """g' sigmoid(alpha g') (u' + 1) with a limit that bites on both sides: the stand-alone kernel and the products that
+    finish it in their epilogues (decode form, prompt form, pairs of SMs)"""
+    from kindi_b200.kernels import linear as L
+    g = torch.Generator().manual_seed(M + F)
+    tdt = DT[dtype]
+    y = (torch.randn(M, width, generator=g)).to(tdt)
+    wg, wu = ((torch.randn(F, width, generator=g) * 0.15).to(tdt) for _ in range(2))
+    wgu, group = L.join_gate_up(wg.cuda(), wu.cuda())
+    for limit, alpha in ((0.8, 1.702), (2.5, 1.0)):
+        gg = torch.clamp(y.double() @ wg.double().T, max=limit)
+        uu = torch.clamp(y.double() @ wu.double().T, min=-limit, max=limit)
+        want = gg * PL.sigmoid(alpha * gg) * (uu + 1.0)
+        ctx = _ctx(M, tdt, fast)
+        got = L.gate_up_glu_clamp(ctx, y.cuda(), wgu, group, F, tdt, limit, alpha)
+        assert int(ctx.status.item()) == 0
+        assert _rel(got, want) < (2e-5 if dtype == "float32" else 1.5e-2), (limit, dtype, fast)
+
+
 @pytest.mark.parametrize("n,top,groups,keep", [(4, 2, 1, 1), (16, 4, 4, 2), (8, 2, 4, 3), (6, 2, 3, 1), (12, 3, 3, 2),
                                                (8, 1, 2, 2), (96, 8, 8, 3), (256, 6, 32, 5), (33, 5, 1, 1)])
 def test_router_pick_within_groups(K, n, top, groups, keep):
