@@ -81,8 +81,12 @@ def gate_up_glu_clamp(ctx, y: torch.Tensor, wgu: torch.Tensor, group: int, f: in
     ``[g | u] = y @ wgu^T`` (``wgu`` as ``join_gate_up`` made it): inside the product where a tensor-core kernel takes
     the shape, else the product as rows or 32-bit planes followed by the kernel of the clamped unit"""
     h = torch.empty((y.shape[0], f), dtype=out_dtype, device=y.device)
+    # (the decode form that finishes the unit itself gives a tile of 128 rows of the joined matrix to at most two CTAs:
+    # a matrix of fewer tiles than half the SMs - a shared expert is small - is faster as split-K planes and the
+    # unit's own kernel: 18 against 31 us at 2688 x 4096 and eight rows)
     if ctx.fast and group == GATE_UP_GROUP and (
-            fast.gemm_swiglu_decode(y, wgu, h, ctx.status, "glu_clamp", (limit, alpha))
+            (wgu.shape[0] >= 128 * (fast.N_SM // 2)
+             and fast.gemm_swiglu_decode(y, wgu, h, ctx.status, "glu_clamp", (limit, alpha)))
             or fast.gemm_swiglu_rows(y, wgu, h, ctx.status, "glu_clamp", (limit, alpha))):
         return h
     gu = rows_or_planes(ctx, y, wgu, out_dtype)
