@@ -306,7 +306,7 @@ def test_experts_with_identity_and_the_clamped_unit(K, dtype, fast, T, width, E,
 
 
 # ------------------------------------------------------------------------------------------- whole models
-CLOSE_CALL = 0.003          # a pick whose choice scores lie closer than this may fall the other way in bfloat16
+CLOSE_CALL = 0.03          # a pick whose choice scores lie closer than this may fall the other way in bfloat16
 
 
 def _plain(folder, reqs):
@@ -322,28 +322,29 @@ def _plain(folder, reqs):
 
 
 def _compare(got, reqs, want, tol, what):
-    """every row within ``tol`` of the plain model's. In bfloat16 the router's logits are products of 16-bit numbers: a
-    row whose pick is a close call on the plain model may pick otherwise (and a later row that rests on it, a probe
-    on a needle, follows), so such rows are left out there - a request whose needle is one, altogether. In 32-bit no
-    row is left out."""
+    """every row within ``tol`` of the plain model's. In bfloat16 the router's inputs carry 16-bit rounding: a row
+    whose pick is a close call on the plain model may pick otherwise, and a flipped expert adds a different branch of
+    unit size, which is no rounding error. There a row may miss the tolerance only if it is such a close call, and
+    few rows may (a request whose needle is a close call is left out altogether: every probe rests on it). In 32-bit
+    no row may."""
     sharp = tol < 1e-3
-    n_out = n_all = 0
+    n_missed = n_all = 0
     for rid, toks in reqs.items():
         z, margin = want[rid]
         mine = np.stack([got[(rid, i)] for i in range(len(toks))])
         n_all += len(toks)
-        keep = np.ones(len(toks), dtype=bool) if sharp else margin >= CLOSE_CALL
-        if not sharp and TL.NEEDLE in toks and not keep[toks.index(TL.NEEDLE)]:
-            n_out += len(toks)
+        close = np.zeros(len(toks), dtype=bool) if sharp else margin < CLOSE_CALL
+        if TL.NEEDLE in toks and close[toks.index(TL.NEEDLE)]:
+            n_missed += len(toks)
             continue
-        n_out += int((~keep).sum())
         err = np.max(np.abs(mine - z), axis=1) / np.max(np.abs(z))
-        err = np.where(keep, err, 0.0)
+        n_missed += int((close & (err > tol)).sum())
+        err = np.where(close, 0.0, err)
         row = int(np.argmax(err))
         assert err[row] <= tol, "%s %s: %.3g at position %d of %d" % (what, rid, err[row], row, len(toks))
         assert sharp or np.median(err) <= TYPICAL, "%s %s: the median row is %.3g off" % (what, rid, np.median(err))
-    assert n_out <= 0.25 * n_all, "%s: %d of %d rows are close calls: the test's routers are not decisive" % (
-        what, n_out, n_all)
+    assert n_missed <= max(2, 0.03 * n_all), "%s: %d of %d rows miss the tolerance after a close call" % (
+        what, n_missed, n_all)
 
 
 def _edge_requests(raw, seed, L=200):
