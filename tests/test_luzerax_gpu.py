@@ -103,7 +103,7 @@ def _scatter_table(lengths, seed, extra=3):
 @pytest.mark.parametrize("dtype,planes", [("float32", 1), ("float32", 3), ("bfloat16", 1), ("bfloat16", 4)])
 @pytest.mark.parametrize("nh,nkv,hd,dim,rot,when,gains,coef,every", [
     (4, 2, 16, 16, 8, "after", False, 0.0, 1), (6, 2, 64, 64, 64, "after", False, 0.0, 1),
-    (8, 4, 128, 48, 0, "before", True, 0.3, 7), (5, 5, 64, 24, 6, "before", True, 1.5, 1),
+    (8, 4, 128, 40, 0, "before", True, 0.3, 7), (5, 5, 64, 24, 6, "before", True, 1.5, 1),
     (3, 1, 24, 24, 24, "none", False, 0.4, 100000), (2, 1, 264, 260, 130, "after", True, 0.0, 1)])
 def test_head_norm_rotation_temperature_and_store(K, dtype, planes, nh, nkv, hd, dim, rot, when, gains, coef, every):
     """every query and key head through its own norm, the rotation and the temperature; queries out, keys and values
