@@ -9,7 +9,8 @@
 // are computed and never stored. CTAs are persistent and take units c, c + gridDim.x, ...; the unit count comes from
 // the plan on the device. Roles as in k_gemm_tc: a producer warp keeps a ring of stages full, one thread issues
 // tcgen05.mma into one of two accumulators in tensor memory, four epilogue warps drain the other with tcgen05.ld.
-//   up form:   H[r][n] = act(D) as bf16 at the sorted row r;
+//   up form:   H[r][n] = act(D) as bf16 at the sorted row r; for gated experts whose rows alternate in groups of 16
+//              gate and 16 up rows, H[r][n / 2] = the finished unit (act(gate) * up, or the clamped unit);
 //   down form: planes[pair % top][pair / top][n] = weight[pair] * D as float, pair = perm[r]: each row goes to
 //              its token's row of the plane of its pick, so the planes' sum in order is the experts' weighted sum.
 #include "sm100.cuh"
@@ -34,7 +35,7 @@ __global__ void __launch_bounds__(MT_THREADS) k_moe_gemm_tc(const __grid_constan
         const __grid_constant__ CUtensorMap mapW, void* __restrict__ C, int ldc, size_t plane_stride, int N, int K,
         const int* KB_STEP_DATA n_tiles, const int* KB_STEP_DATA tile_e, const int* KB_STEP_DATA tile_r0,
         const int* KB_STEP_DATA offs, const int* KB_STEP_DATA perm, const float* KB_STEP_DATA wts, int top, int act,
-        int* status) {
+        int* status, KbGate glu) {
     using S = MoeSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -150,7 +151,27 @@ __global__ void __launch_bounds__(MT_THREADS) k_moe_gemm_tc(const __grid_constan
                 tmem_ld_wait();
                 if (!live) continue;
                 const int g0 = q0 + c0;
-                if (UP) {
+                if (UP && glu.act != 0) {
+                    // gated experts whose unit is finished here: the expert's rows come in groups of 16 gate rows and
+                    // the 16 up rows of the same outputs (N a multiple of 32), so this piece holds 16 whole outputs
+                    bf16* dst = (bf16*)crow + (g0 >> 1);
+                    if ((((uintptr_t)dst) & 15) == 0) {
+                        uint32_t h[8];
+#pragma unroll
+                        for (int c = 0; c < 8; c++) {
+                            __nv_bfloat162 p = __floats2bfloat162_rn(
+                                kb_glu_fast(__uint_as_float(v[2 * c]), __uint_as_float(v[16 + 2 * c]), glu),
+                                kb_glu_fast(__uint_as_float(v[2 * c + 1]), __uint_as_float(v[16 + 2 * c + 1]), glu));
+                            h[c] = *(uint32_t*)&p;
+                        }
+                        *(uint4*)(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *(uint4*)(dst + 8) = make_uint4(h[4], h[5], h[6], h[7]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; c++)
+                            dst[c] = __float2bfloat16_rn(kb_glu_fast(__uint_as_float(v[c]), __uint_as_float(v[16 + c]), glu));
+                    }
+                } else if (UP) {
                     bf16* dst = (bf16*)crow + g0;
                     if (g0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -213,7 +234,7 @@ template <int BN, int STAGES, bool UP>
 static int launch_moe_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int ldc, long long plane_stride, int N,
                          int K, int max_tiles, const int* n_tiles, const int* tile_e, const int* tile_r0,
                          const int* offs, const int* perm, const float* wts, int top, int act, int* status,
-                         cudaStream_t st) {
+                         cudaStream_t st, KbGate glu) {
     using S = MoeSmem<BN, STAGES>;
     auto kern = k_moe_gemm_tc<BN, STAGES, UP>;
     static char once_tag;
@@ -224,7 +245,7 @@ static int launch_moe_tc(const CUtensorMap& ma, const CUtensorMap& mw, void* C, 
     const long long units = (long long)max_tiles * ((N + BN - 1) / BN);
     const int grid = units < moe_sm_count() ? (int)units : moe_sm_count();
     kb_launch(kern, grid, MT_THREADS, S::TOTAL, st, ma, mw, C, ldc, (size_t)plane_stride, N, K, n_tiles, tile_e,
-              tile_r0, offs, perm, wts, top, act, status);
+              tile_r0, offs, perm, wts, top, act, status, glu);
     return (int)cudaGetLastError();
 }
 
@@ -233,21 +254,28 @@ extern "C" int kb_moe_gemm_tc_tile() { return MT_BM; }
 
 // A: sorted rows [n_rows][K] bf16 (row stride lda); W: [E * N][K] bf16, contiguous. up != 0: C = H [n_rows][ldc] bf16;
 // else C = planes (float) with row stride ldc and plane_stride elements between planes. bn: 64, 128 or 256.
+// glu != 0 (up form, N a multiple of 32): every expert's rows are 16 gate rows, then the 16 up rows of the same outputs,
+// group after group; `act` names the gated unit (KB_ACT_SILU, KB_ACT_GELU_TANH, or KB_ACT_GLU_CLAMP with its limit and
+// alpha) and C = H [n_rows][N / 2] holds the finished unit.
 extern "C" int kb_moe_gemm_tc(const void* A, int n_rows, int lda, const void* W, int E, int N, int K, void* C, int ldc,
                               long long plane_stride, int max_tiles, const int* n_tiles, const int* tile_e,
                               const int* tile_r0, const int* offs, const int* perm, const float* wts, int top, int act,
-                              int up, int bn, int* status, cudaStream_t st) {
+                              int up, int bn, int* status, cudaStream_t st, int glu = 0, float act_lim = 0.0f,
+                              float act_alpha = 0.0f) {
     if (n_rows <= 0 || max_tiles <= 0 || N <= 0 || K <= 0) return 0;
     if ((K % 8) || (lda % 8)) return (int)cudaErrorInvalidValue;
+    if (glu && (!up || (N % 32))) return (int)cudaErrorInvalidValue;
+    KbGate gate = kb_gate_of(act, act_lim, act_alpha);
+    if (!glu) gate.act = 0;
     CUtensorMap ma, mw;
     int rc;
     if ((rc = kb_make_map_bf16(&ma, A, (uint64_t)n_rows, K, lda, MT_BM))) return rc;
     if ((rc = kb_make_map_bf16(&mw, W, (uint64_t)E * N, K, K, bn))) return rc;
 #define MT_GO(BN, ST)                                                                                             \
     return up ? launch_moe_tc<BN, ST, true>(ma, mw, C, ldc, plane_stride, N, K, max_tiles, n_tiles, tile_e, tile_r0, \
-                                            offs, perm, wts, top, act, status, st)                                \
+                                            offs, perm, wts, top, act, status, st, gate)                          \
               : launch_moe_tc<BN, ST, false>(ma, mw, C, ldc, plane_stride, N, K, max_tiles, n_tiles, tile_e,      \
-                                             tile_r0, offs, perm, wts, top, act, status, st)
+                                             tile_r0, offs, perm, wts, top, act, status, st, gate)
     switch (bn) {
         case 64: MT_GO(64, 6);
         case 128: MT_GO(128, 6);

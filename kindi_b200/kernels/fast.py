@@ -308,7 +308,12 @@ def _moe_tc_ok(y, wup, wdown) -> bool:
 def _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T, gated=False, weight_on="output", act_params=None):
     E, F, width = wup.shape
     h = torch.empty((T * top, F), dtype=torch.bfloat16, device=ys.device)
-    if gated:
+    if gated and act == "glu_clamp" and weight_on == "output" and act_params[2] == 16 and F % 32 == 0:
+        # the clamped unit is finished in the up product's epilogue (gate and up rows alternate in groups of 16)
+        h = torch.empty((T * top, F // 2), dtype=torch.bfloat16, device=ys.device)
+        K.moe_gemm_tc(ys, wup, h, plan, None, top, act, up=True, bn=_moe_bn(F, T * top), status=ctx.status, glu=True,
+                      act_params=act_params)
+    elif gated:
         # [gate | up] of every pair, then act(w g) * (w u) with the pick's weight on the expert's input (or 1)
         K.moe_gemm_tc(ys, wup, h, plan, None, top, "none", up=True, bn=_moe_bn(F, T * top), status=ctx.status)
         gu, h = h, torch.empty((T * top, F // 2), dtype=torch.bfloat16, device=ys.device)

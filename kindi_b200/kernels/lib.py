@@ -97,7 +97,7 @@ _SIGS = {
     "kb_moe_gemm_tc_tile": [],
     "kb_moe_gemm_tc": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int,
                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                       c_void_p, c_void_p],
+                       c_void_p, c_void_p, c_int, c_float, c_float],
     "kb_moe_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "kb_moe_gemm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int,
                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -635,16 +635,21 @@ def moe_gather(y: torch.Tensor, out: torch.Tensor, plan: MoePlan, top: int) -> N
 
 
 def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: MoePlan, wts: Optional[torch.Tensor],
-                top: int, act: str, *, up: bool, bn: int, status: torch.Tensor) -> None:
+                top: int, act: str, *, up: bool, bn: int, status: torch.Tensor, glu: bool = False,
+                act_params=None) -> None:
     """the experts' grouped product on the tensor cores over the plan's tiles of 128 sorted rows. a: sorted rows
     [n_pairs, K] bf16; w [E, N, K] bf16. up: out = act(a w[e]^T) as bf16 [n_pairs, N]; else out = float planes
-    [top, T, N] with plane k of a row's token = its k-th weight * (a w[e]^T)"""
+    [top, T, N] with plane k of a row's token = its k-th weight * (a w[e]^T). ``glu`` (up form): every expert's rows
+    are 16 gate rows then the 16 up rows of the same outputs, group after group, ``act`` names the gated unit (a key of
+    ``GATE_ACT``, with ``act_params``) and out [n_pairs, N / 2] holds the finished unit"""
     _need_cuda(a, w, out, wts)
     E, N, Kd = w.shape
     assert a.dtype == w.dtype == torch.bfloat16 and a.shape == (plan.n_pairs, Kd) and a.stride(1) == 1
     assert w.is_contiguous() and plan.tile == moe_gemm_tc_tile() and bn in (64, 128, 256)
     if up:
-        assert out.dtype == torch.bfloat16 and out.shape == (plan.n_pairs, N) and out.stride(1) == 1
+        n_out = N // 2 if glu else N
+        assert not glu or N % 32 == 0
+        assert out.dtype == torch.bfloat16 and out.shape == (plan.n_pairs, n_out) and out.stride(1) == 1
         ldc, pstride = out.stride(0), 0
     else:
         assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[0] == top and out.shape[2] == N
@@ -652,7 +657,8 @@ def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: MoePl
         ldc, pstride = N, out.stride(0)
     _check(load().kb_moe_gemm_tc(_p(a), plan.n_pairs, a.stride(0), _p(w), E, N, Kd, _p(out), ldc, pstride,
                                  plan.max_tiles, _p(plan.n_tiles), _p(plan.tile_e), _p(plan.tile_r0), _p(plan.offs),
-                                 _p(plan.perm), _p(wts), top, ACT[act], 1 if up else 0, bn, _p(status), _stream()),
+                                 _p(plan.perm), _p(wts), top, GATE_ACT[act] if glu else ACT[act], 1 if up else 0, bn,
+                                 _p(status), _stream(), 1 if glu else 0, *_gate_params(act if glu else "", act_params)),
            "moe_gemm_tc")
 
 

@@ -26,12 +26,13 @@ def feed_forward(ctx, y: torch.Tensor, wr: torch.Tensor, br: Optional[torch.Tens
 
 def gate_mul(gu: torch.Tensor, wts: Optional[torch.Tensor], plan, act: str, h: torch.Tensor, act_params=None) -> None:
     """the gated experts' ``act(g) * u`` over the plan's sorted rows ``gu`` = [gate | up]; ``act`` "glu_clamp" with
-    ``act_params`` = (limit, alpha): ``g' sigmoid(alpha g') (u' + 1)``, gate clamped from above, up from both sides"""
+    ``act_params`` = (limit, alpha, group): ``g' sigmoid(alpha g') (u' + 1)``, gate clamped from above, up from both
+    sides; the expert's gate and up columns alternate in groups of ``group`` (the inner size: all gates, then all ups)"""
     if act == "glu_clamp":
         if wts is not None:
             raise ValueError("a weight on the input of experts with the clamped unit")
-        limit, alpha = act_params
-        K.glu_clamp(gu, h, h.shape[1], limit, alpha)
+        limit, alpha, group = act_params
+        K.glu_clamp(gu, h, group, limit, alpha)
     else:
         K.moe_gate_mul(gu, wts, plan, act, h)
 

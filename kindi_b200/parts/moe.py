@@ -102,7 +102,10 @@ class MixtureOfExperts(FeedForward):
         if self.act not in K.ACT and not (self.act == "glu_clamp" and spec.get("gated")):
             raise ValueError("unknown activation %r; known: %s, and glu_clamp for gated experts"
                              % (self.act, ", ".join(sorted(K.ACT))))
-        self.act_params = (float(spec["limit"]), float(spec.get("alpha", 1.702))) if self.act == "glu_clamp" else None
+        # (the clamped unit's gate and up rows alternate in groups that the products' epilogues can finish, like a dense
+        # gated feed-forward's)
+        self.act_params = (float(spec["limit"]), float(spec.get("alpha", 1.702)),
+                           L.GATE_UP_GROUP if self.f % L.GATE_UP_GROUP == 0 else self.f) if self.act == "glu_clamp" else None
         self.n_identity = int(spec.get("identity") or 0)
         self.n_out = self.E + self.n_identity
         n = self._names(spec)
@@ -147,7 +150,10 @@ class MixtureOfExperts(FeedForward):
             gates = [weights(n["gate"] % e) for e in range(self.E)]
             if {w.dtype for w in gates} != {ups[0].dtype}:
                 raise ValueError("the expert weights of %s are stored in different dtypes" % weights.prefix)
-            ups = [torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]      # every expert: its gate rows, then up
+            if self.act == "glu_clamp":
+                ups = [L.join_gate_up(g, u)[0] for g, u in zip(gates, ups)]   # gate and up rows in groups of 16 (or all)
+            else:
+                ups = [torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]  # every expert: its gate rows, then up
         self.wup = torch.stack(ups).contiguous()            # [E, f (gated: 2 f), width]
         self.wdown = torch.stack(downs).contiguous()        # [E, width, f]
         self.shared = None
