@@ -291,6 +291,9 @@ def attention_decode_rope(ctx, qkv, out, nh, nkv, hd, scale, window, inv_freq, r
     return True
 
 
+MOE_GLU_MIN_PAIRS = 512     # (row, pick) pairs from which the grouped up product finishes a gated unit itself
+
+
 def _moe_bn(n: int, n_pairs: int) -> int:
     """columns of a unit: the widest tile the expert's matrix fills. Measured at widths 1024 to 4096 with experts of 512
     to 2048: 256 columns are as fast or faster than 128 for a 2048-token step (experts of 2048: 171 against 199 us) and
@@ -308,8 +311,12 @@ def _moe_tc_ok(y, wup, wdown) -> bool:
 def _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T, gated=False, weight_on="output", act_params=None):
     E, F, width = wup.shape
     h = torch.empty((T * top, F), dtype=torch.bfloat16, device=ys.device)
-    if gated and act == "glu_clamp" and weight_on == "output" and act_params[2] == 16 and F % 32 == 0:
-        # the clamped unit is finished in the up product's epilogue (gate and up rows alternate in groups of 16)
+    if (gated and act == "glu_clamp" and weight_on == "output" and act_params[2] == 16 and F % 32 == 0
+            and T * top >= MOE_GLU_MIN_PAIRS):
+        # the clamped unit is finished in the up product's epilogue (gate and up rows alternate in groups of 16). A
+        # decode-sized step keeps the unit's own kernel: its tiles hold a row or two, the longer epilogue sits on the
+        # step's critical path while the small kernel hides behind its neighbours (batch 8, three picks: 0.374 against
+        # 0.363 ms a step at width 1024, 1.064 against 1.056 at 4096; a 2048-token prompt 1.57 against 1.65 ms)
         h = torch.empty((T * top, F // 2), dtype=torch.bfloat16, device=ys.device)
         K.moe_gemm_tc(ys, wup, h, plan, None, top, act, up=True, bn=_moe_bn(F, T * top), status=ctx.status, glu=True,
                       act_params=act_params)
